@@ -33,7 +33,7 @@ NO_PAGE = -1
 class CacheGroup:
     index: int
     need: object                       # PagedKV or FixedState
-    entries: list                      # run-entry indices that own a cache in this group
+    entries: list                      # owners of a cache in this group: run-entry indices, or (run entry, role)
     pool: PagePool | None = None       # paged groups only
     max_blocks: int = 0
     table: np.ndarray | None = None    # [max_requests, max_blocks] int32, NO_PAGE where nothing is held
@@ -54,10 +54,16 @@ class _Request:
 
 def group_entries(needs) -> list:
     """Group run entries by what they keep.  ``needs[i]`` is the need of run
-    entry i, or None if the entry reads another entry's cache."""
+    entry i, or None if the entry reads another entry's cache, or ``{role: need}`` if several
+    parts of the entry's layer keep something: each (entry, role) then owns a cache."""
     groups: dict = {}
     for entry, need in enumerate(needs):
         if need is None or isinstance(need, NoCache):
+            continue
+        if isinstance(need, dict):
+            for role, one in need.items():
+                if one is not None and not isinstance(one, NoCache):
+                    groups.setdefault(one, []).append((entry, role))
             continue
         groups.setdefault(need, []).append(entry)
     return [(need, entries) for need, entries in groups.items()]
@@ -72,7 +78,7 @@ class CacheManager:
         self.max_requests = int(max_requests)
         self.max_tokens_per_request = int(max_tokens_per_request)
         self.groups: list[CacheGroup] = []
-        self.entry_group: dict[int, tuple] = {}        # run entry -> (group index, index within the group)
+        self.entry_group: dict = {}                    # run entry, or (run entry, role) -> (group index, index within the group)
         max_blocks = -(-self.max_tokens_per_request // self.page_size)
         for index, (need, entries) in enumerate(group_entries(needs)):
             group = CacheGroup(index, need, entries)

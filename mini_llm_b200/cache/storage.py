@@ -49,6 +49,19 @@ class StateLayerCache(LayerCache):
         self.writes = writes
 
 
+class CompositeLayerCache(LayerCache):
+    """The caches of a run entry whose layer has several parts that keep something."""
+
+    kind = "composite"
+
+    def __init__(self, by_role: dict):
+        self.by_role = by_role
+        self.writes = all(view.writes for view in by_role.values())
+
+    def of(self, role: str):
+        return self.by_role.get(role) or LayerCache()
+
+
 class CacheStorage:
     def __init__(self, manager, order, dtype: torch.dtype, device, max_items: int, poison: float | None = None):
         """``poison``: a debugging value.  Every page slot holds it until a token is stored
@@ -70,35 +83,50 @@ class CacheStorage:
                          group.need.head_size)
                 fill = 0.0 if poison is None else poison
                 self.keys[group.index] = torch.full(shape, fill, dtype=dtype, device=device)
-                self.values[group.index] = torch.full(shape, fill, dtype=dtype, device=device)
+                if group.need.has_values:
+                    self.values[group.index] = torch.full(shape, fill, dtype=dtype, device=device)
                 self.block_tables[group.index] = torch.zeros((self.max_items, group.max_blocks), dtype=torch.int32,
                                                              device=device)
             elif isinstance(group.need, FixedState):
-                shape = (n_entries, manager.max_requests, *group.need.shape)
+                # one slot beyond the last request's: steps that are filled up to a round shape
+                # let their filler tokens keep their state there
+                shape = (n_entries, manager.max_requests + 1, *group.need.shape)
                 self.states[group.index] = torch.zeros(shape, dtype=_STATE_DTYPES[group.need.dtype], device=device)
+        def view_of(key, writes):
+            g, position = manager.entry_group[key]
+            if manager.groups[g].paged:
+                values = self.values[g][position] if g in self.values else None
+                return PagedLayerCache(g, self.keys[g][position], values, self.block_tables[g], manager.page_size, writes)
+            return StateLayerCache(g, self.states[g][position], writes)
+
         self.views = []
         for index, entry in enumerate(order):
             owner = index if entry.cache_of is None else entry.cache_of
-            if owner not in manager.entry_group:
-                self.views.append(LayerCache())
-                continue
-            g, position = manager.entry_group[owner]
-            group = manager.groups[g]
             writes = entry.cache_of is None
-            if group.paged:
-                self.views.append(PagedLayerCache(g, self.keys[g][position], self.values[g][position],
-                                                  self.block_tables[g], manager.page_size, writes))
+            roles = [key[1] for key in manager.entry_group if isinstance(key, tuple) and key[0] == owner]
+            if owner in manager.entry_group:
+                self.views.append(view_of(owner, writes))
+            elif roles:
+                self.views.append(CompositeLayerCache({role: view_of((owner, role), writes) for role in roles}))
             else:
-                self.views.append(StateLayerCache(g, self.states[g][position], writes))
+                self.views.append(LayerCache())
 
         if poison is not None:
             manager.on_free = self.poison_pages
+
+    def paged_views(self):
+        """Every paged view, also those inside the caches of entries with several."""
+        for view in self.views:
+            for one in (view.by_role.values() if view.kind == "composite" else (view,)):
+                if one.kind == "paged":
+                    yield one
 
     def poison_pages(self, group_index: int, pages) -> None:
         """Overwrite pages that went back to their pool (debugging engines only)."""
         index = torch.tensor(list(pages), dtype=torch.int64, device=self.device)
         for store in (self.keys, self.values):
-            store[group_index].index_fill_(1, index, self.poison)
+            if group_index in store:
+                store[group_index].index_fill_(1, index, self.poison)
 
     def read_tokens(self, view_index: int, slot: int, first: int, count: int):
         """Keys and values of tokens ``first .. first + count - 1`` of the request in ``slot``
@@ -106,6 +134,8 @@ class CacheStorage:
         gathered through the block table (the reference's test hook copies a layer's rows
         out of its contiguous cache, engine/src/gpt2_gpu.cu:185-195)."""
         view = self.views[view_index]
+        if view.kind == "composite":
+            view = next((v for v in view.by_role.values() if v.kind == "paged"), view)
         if view.kind != "paged":
             raise ValueError(f"run entry {view_index} keeps no paged keys and values")
         page_size = self.manager.page_size
@@ -115,7 +145,8 @@ class CacheStorage:
         if count and int(pages.min()) < 0:
             raise ValueError(f"slot {slot} holds no page for some of tokens {first}..{first + count - 1}")
         pages, within = pages.to(self.device), (positions % page_size).to(self.device)
-        return view.k_pages[pages, within].clone(), view.v_pages[pages, within].clone()
+        return (view.k_pages[pages, within].clone(),
+                view.v_pages[pages, within].clone() if view.v_pages is not None else None)
 
     def reset_slot(self, slot: int) -> None:
         """Fixed-size state starts at zero for a new request."""

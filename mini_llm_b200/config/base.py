@@ -84,15 +84,17 @@ class ModelConfig:
 
 
 def architecture_name(raw: dict) -> str:
-    """The name ``config.json`` gives its model class: ``architectures[0]``,
-    or, when that list is absent, ``model_type``."""
+    """The name ``config.json`` gives its model class: ``architectures[0]``, or the string
+    ``architecture``, or, when both are absent, ``model_type``."""
     archs = raw.get("architectures")
     if isinstance(archs, list) and archs and isinstance(archs[0], str):
         return archs[0]
+    if isinstance(raw.get("architecture"), str):
+        return raw["architecture"]
     model_type = raw.get("model_type")
     if isinstance(model_type, str):
         return "model_type:" + model_type
-    raise ConfigError("config.json names no architecture: neither 'architectures' nor 'model_type' is set")
+    raise ConfigError("config.json names no architecture: none of 'architectures', 'architecture' and 'model_type' is set")
 
 
 def read_config_json(model_dir: str) -> dict:

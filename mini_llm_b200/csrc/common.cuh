@@ -23,7 +23,9 @@ enum { DT_F32 = 0, DT_BF16 = 1 };
 //   EPI_GELU_TANH  out = gelu_tanh(acc + bias)
 //   EPI_GELU_ERF   out = gelu_erf(acc + bias)
 //   EPI_ADD        out(fp32) += acc + bias        (residual sum kept in 32-bit)
-enum { EPI_STORE = 0, EPI_GELU_TANH = 1, EPI_GELU_ERF = 2, EPI_ADD = 3 };
+//   EPI_RELU_SQ    out = max(acc + bias, 0)^2
+//   EPI_SILU       out = u / (1 + exp(-u)), u = acc + bias
+enum { EPI_STORE = 0, EPI_GELU_TANH = 1, EPI_GELU_ERF = 2, EPI_ADD = 3, EPI_RELU_SQ = 4, EPI_SILU = 5 };
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
@@ -60,6 +62,8 @@ __device__ __forceinline__ float gelu_tanh_fast(float u) {
 template <int EPI> __device__ __forceinline__ float apply_activation(float v) {
     if (EPI == EPI_GELU_TANH) return gelu_tanh_f(v);
     if (EPI == EPI_GELU_ERF) return gelu_erf_f(v);
+    if (EPI == EPI_RELU_SQ) return v > 0.0f ? v * v : 0.0f;
+    if (EPI == EPI_SILU) return v / (1.0f + expf(-v));
     return v;
 }
 

@@ -194,6 +194,8 @@ static int launch_linear_plain(void* out, const void* a, const void* w, const fl
     case EPI_GELU_TANH: linear_plain_kernel<AT, WT, OT, EPI_GELU_TANH><<<grid, 256, 0, s>>>(o, ap, wp, bias, M, N, K, lda, ldo); break;
     case EPI_GELU_ERF: linear_plain_kernel<AT, WT, OT, EPI_GELU_ERF><<<grid, 256, 0, s>>>(o, ap, wp, bias, M, N, K, lda, ldo); break;
     case EPI_ADD: linear_plain_kernel<AT, WT, OT, EPI_ADD><<<grid, 256, 0, s>>>(o, ap, wp, bias, M, N, K, lda, ldo); break;
+    case EPI_RELU_SQ: linear_plain_kernel<AT, WT, OT, EPI_RELU_SQ><<<grid, 256, 0, s>>>(o, ap, wp, bias, M, N, K, lda, ldo); break;
+    case EPI_SILU: linear_plain_kernel<AT, WT, OT, EPI_SILU><<<grid, 256, 0, s>>>(o, ap, wp, bias, M, N, K, lda, ldo); break;
     default: return fail("linear: unknown epilogue");
     }
     return check_launch("linear_plain_kernel");

@@ -1,0 +1,594 @@
+// Kernels of the mixers that are no softmax attention over keys and values per head, and of
+// what stands around them: norms by root mean square in groups (also as the way a
+// sublayer's result is added onto the residual stream, and with a sigmoid gate), a short
+// causal convolution over time with its state, rotary positions in the interleaved layout,
+// attention over a shared latent (all heads read one row per token; the row's first part is
+// also the value), a batch of small products per head, the matrix-memory recurrence
+// S <- a S + b k v^T with a fixed or a gated and stabilised decay, and the weighted sum of
+// all layer results.
+//
+// Every kernel is templated on the element type of the activations (float: the true 32-bit
+// path; bfloat16: the serving path).  Norm statistics, angles, scores, softmax, gates, decays
+// and all recurrent state are 32-bit in both.  A step's entries are read from device arrays
+// (slot, first row, rows, first position per entry), so a step of one shape launches the same
+// kernels with the same arguments.
+#include "common.cuh"
+
+MLLM_DEFINE_ERROR_API(mllm_sequence)
+
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float log_sigmoid_f(float z) {
+    return z >= 0.0f ? -log1pf(expf(-z)) : z - log1pf(expf(z));
+}
+
+// ---------------------------------------------------------------------------
+// Norm by root mean square in groups.  Row r of x (fp32) is cut into `groups` equal
+// consecutive pieces; each is divided by sqrt(mean(piece^2) + eps); the whole is multiplied
+// by the gain.  One block per (row, group).
+//   ADD   out (fp32) += result            (a sublayer's result onto the residual stream)
+//   GATE  result *= sigmoid(gate[r, c])   (gate has the activations' element type)
+// `rows` (may be null) gathers input rows.  out may be x itself.
+// ---------------------------------------------------------------------------
+template <typename O, typename G, bool ADD, bool GATE>
+__global__ void grouped_rms_norm_kernel(O* __restrict__ out, long ld_out, const float* x, long ld_x,
+                                        const float* __restrict__ gain, const int* __restrict__ rows,
+                                        const G* __restrict__ gate, long ld_gate, int size, float eps) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x, g = blockIdx.y;
+    const float* part = x + (long)(rows ? rows[r] : r) * ld_x + (long)g * size;
+    float sq = 0.0f;
+    for (int d = threadIdx.x; d < size; d += blockDim.x) sq = fmaf(part[d], part[d], sq);
+    const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)size + eps);
+    for (int d = threadIdx.x; d < size; d += blockDim.x) {
+        const int c = g * size + d;
+        float v = part[d] * inv * gain[c];
+        if (GATE) v *= sigmoid_f(to_f32(gate[(long)r * ld_gate + c]));
+        O* o = out + (long)r * ld_out + c;
+        if (ADD) *o = from_f32<O>(to_f32(*o) + v);
+        else *o = from_f32<O>(v);
+    }
+}
+
+template <typename O, typename G>
+static void launch_grouped_rms_norm(void* out, long ld_out, const float* x, long ld_x, const float* gain, const int* rows,
+                                    const void* gate, long ld_gate, int n_rows, int size, int groups, float eps, int add,
+                                    cudaStream_t s) {
+    const int threads = size >= 1024 ? 256 : (size >= 256 ? 128 : (size >= 64 ? 64 : 32));
+    dim3 grid(n_rows, groups);
+    O* o = (O*)out;
+    const G* g = (const G*)gate;
+    if (add) grouped_rms_norm_kernel<O, G, true, false><<<grid, threads, 0, s>>>(o, ld_out, x, ld_x, gain, rows, g, ld_gate, size, eps);
+    else if (gate != nullptr) grouped_rms_norm_kernel<O, G, false, true><<<grid, threads, 0, s>>>(o, ld_out, x, ld_x, gain, rows, g, ld_gate, size, eps);
+    else grouped_rms_norm_kernel<O, G, false, false><<<grid, threads, 0, s>>>(o, ld_out, x, ld_x, gain, rows, g, ld_gate, size, eps);
+}
+
+// out_dtype / gate_dtype: element types of out and gate.  add != 0: out is fp32 and is added to.
+extern "C" int mllm_sequence_grouped_rms_norm(void* out, long ld_out, const float* x, long ld_x, const float* gain,
+                                              const int* rows, const void* gate, long ld_gate, int n_rows, int width,
+                                              int groups, float eps, int add, int out_dtype, int gate_dtype, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (groups <= 0 || width <= 0 || width % groups != 0) return fail("grouped_rms_norm: the width is not a multiple of the groups");
+    if (groups > 65535) return fail("grouped_rms_norm: too many groups for one launch");
+    if (add && (out_dtype != DT_F32 || gate != nullptr)) return fail("grouped_rms_norm: the residual sum is 32-bit and takes no gate");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int size = width / groups;
+    if (out_dtype == DT_F32 && (gate == nullptr || gate_dtype == DT_F32))
+        launch_grouped_rms_norm<float, float>(out, ld_out, x, ld_x, gain, rows, gate, ld_gate, n_rows, size, groups, eps, add, s);
+    else if (out_dtype == DT_BF16 && (gate == nullptr || gate_dtype == DT_BF16))
+        launch_grouped_rms_norm<bf16, bf16>(out, ld_out, x, ld_x, gain, rows, gate, ld_gate, n_rows, size, groups, eps, add, s);
+    else if (out_dtype == DT_F32 && gate_dtype == DT_BF16)
+        launch_grouped_rms_norm<float, bf16>(out, ld_out, x, ld_x, gain, rows, gate, ld_gate, n_rows, size, groups, eps, add, s);
+    else
+        return fail("grouped_rms_norm: unsupported combination of element types");
+    return check_launch("grouped_rms_norm_kernel");
+}
+
+// ---------------------------------------------------------------------------
+// Short causal convolution over time, per channel, added onto its input:
+//   out[t, c] = h[t, c] + sum_{j < taps} w[c, j] * h[t - (taps - 1) + j, c]
+// over the tokens of one request; inputs before this step's portion come from the request's
+// state (the last taps - 1 inputs, oldest first, zero before the sequence's start).
+// One block per token.  A second kernel (one block per entry) then moves the state on.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void causal_taps_kernel(T* __restrict__ out, const T* __restrict__ h, const float* __restrict__ w,
+                                   const float* __restrict__ state, long state_stride, const int* __restrict__ positions,
+                                   const int* __restrict__ token_item, const int* __restrict__ item_slot,
+                                   const int* __restrict__ item_start, int width, int taps) {
+    const int t = blockIdx.x;
+    const int item = token_item[t];
+    const int local = positions[t] - item_start[item];          // tokens of this request before t in this step
+    const float* held = state + (long)item_slot[item] * state_stride;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float mine = to_f32(h[(long)t * width + c]);
+        float acc = mine;
+        for (int back = taps - 1; back >= 1; back--) {
+            float v;
+            if (local - back >= 0) v = to_f32(h[(long)(t - back) * width + c]);
+            else v = held[(long)(taps - 1 + local - back) * width + c];
+            acc = fmaf(w[(long)c * taps + (taps - 1 - back)], v, acc);
+        }
+        acc = fmaf(w[(long)c * taps + taps - 1], mine, acc);
+        out[(long)t * width + c] = from_f32<T>(acc);
+    }
+}
+
+template <typename T>
+__global__ void causal_taps_state_kernel(float* __restrict__ state, long state_stride, const T* __restrict__ h,
+                                         const int* __restrict__ item_slot, const int* __restrict__ item_offset,
+                                         const int* __restrict__ item_count, int width, int taps) {
+    const int item = blockIdx.x;
+    const int count = item_count[item];
+    if (count <= 0) return;
+    float* held = state + (long)item_slot[item] * state_stride;
+    const long first = item_offset[item];
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        // ascending: entry s takes what lay at s + count, which no earlier write has touched
+        for (int s = 0; s < taps - 1; s++) {
+            const int from = count - (taps - 1) + s;             // index among this step's tokens
+            held[(long)s * width + c] = from >= 0 ? to_f32(h[(first + from) * width + c])
+                                                  : held[(long)(s + count) * width + c];
+        }
+    }
+}
+
+extern "C" int mllm_sequence_causal_taps(void* out, const void* h, const float* w, float* state, long state_stride,
+                                         const int* positions, const int* token_item, const int* item_slot,
+                                         const int* item_start, const int* item_offset, const int* item_count,
+                                         int n_tokens, int n_items, int width, int taps, int writes, int dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (taps < 1) return fail("causal_taps: at least one tap");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = width >= 256 ? 256 : 64;
+    if (dtype == DT_F32) {
+        causal_taps_kernel<float><<<n_tokens, threads, 0, s>>>((float*)out, (const float*)h, w, state, state_stride, positions,
+                                                               token_item, item_slot, item_start, width, taps);
+        if (writes && taps > 1)
+            causal_taps_state_kernel<float><<<n_items, threads, 0, s>>>(state, state_stride, (const float*)h, item_slot,
+                                                                        item_offset, item_count, width, taps);
+    } else if (dtype == DT_BF16) {
+        causal_taps_kernel<bf16><<<n_tokens, threads, 0, s>>>((bf16*)out, (const bf16*)h, w, state, state_stride, positions,
+                                                              token_item, item_slot, item_start, width, taps);
+        if (writes && taps > 1)
+            causal_taps_state_kernel<bf16><<<n_items, threads, 0, s>>>(state, state_stride, (const bf16*)h, item_slot,
+                                                                       item_offset, item_count, width, taps);
+    } else {
+        return fail("causal_taps: unknown dtype");
+    }
+    return check_launch("causal_taps_kernel");
+}
+
+// ---------------------------------------------------------------------------
+// What latent attention keeps of a token, and its queries' rotated parts.
+//   down[t] = [rank values | rot values] (fp32): the first are divided by their root mean
+//   square and multiplied by `gain` (the latent), the last get rotary positions (the key part
+//   all heads share).  Both go into the token's row of the cache pages, [rank + rot] wide.
+//   q[t] = per head [dim | rot]: the rot part gets rotary positions and goes, in 32-bit, to
+//   q_eff[t, head, rank .. rank + rot) (the first `rank` entries of q_eff are filled by the
+//   product with the key expansion).
+// Rotary positions, interleaved: among the first rot_dims entries, (x[2i], x[2i+1]) turns by
+// position * inv_freq[i]; the rest pass unchanged.  Angles in 64-bit.
+// One block per token.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void latent_prepare_kernel(T* __restrict__ pages, float* __restrict__ q_eff, const float* __restrict__ down,
+                                      const T* __restrict__ q, long ld_q, const float* __restrict__ gain,
+                                      const double* __restrict__ inv_freq, const int* __restrict__ positions,
+                                      const int* __restrict__ token_item, const int* __restrict__ block_table,
+                                      int max_blocks, int page_size, int rank, int rot, int rot_dims, int heads, int dim,
+                                      float eps, int writes) {
+    __shared__ float scratch[33];
+    extern __shared__ float turn[];                  // cos[rot_dims / 2], sin[rot_dims / 2]
+    const int t = blockIdx.x;
+    const int p = positions[t];
+    const int half = rot_dims / 2;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        double s, c;
+        sincos((double)p * inv_freq[i], &s, &c);
+        turn[i] = (float)c;
+        turn[half + i] = (float)s;
+    }
+    const float* mine = down + (long)t * (rank + rot);
+    float sq = 0.0f;
+    for (int d = threadIdx.x; d < rank; d += blockDim.x) sq = fmaf(mine[d], mine[d], sq);
+    const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)rank + eps);      // (its barriers also publish turn[])
+    if (writes) {
+        const int page = block_table[(long)token_item[t] * max_blocks + p / page_size];
+        T* row = pages + ((long)page * page_size + (p % page_size)) * (rank + rot);
+        for (int d = threadIdx.x; d < rank; d += blockDim.x) row[d] = from_f32<T>(mine[d] * inv * gain[d]);
+        for (int e = threadIdx.x; e < rot; e += blockDim.x) {
+            float v = mine[rank + e];
+            if (e < 2 * half) {
+                const float c = turn[e >> 1], s = turn[half + (e >> 1)];
+                v = (e & 1) ? v * c + mine[rank + e - 1] * s : v * c - mine[rank + e + 1] * s;
+            }
+            row[rank + e] = from_f32<T>(v);
+        }
+    }
+    for (int i = threadIdx.x; i < heads * rot; i += blockDim.x) {
+        const int head = i / rot, e = i % rot;
+        const T* from = q + (long)t * ld_q + (long)head * (dim + rot) + dim;
+        float v = to_f32(from[e]);
+        if (e < 2 * half) {
+            const float c = turn[e >> 1], s = turn[half + (e >> 1)];
+            v = (e & 1) ? v * c + to_f32(from[e - 1]) * s : v * c - to_f32(from[e + 1]) * s;
+        }
+        q_eff[((long)t * heads + head) * (rank + rot) + rank + e] = v;
+    }
+}
+
+extern "C" int mllm_sequence_latent_prepare(void* pages, float* q_eff, const float* down, const void* q, long ld_q,
+                                            const float* gain, const double* inv_freq, const int* positions,
+                                            const int* token_item, const int* block_table, int max_blocks, int page_size,
+                                            int n_tokens, int rank, int rot, int rot_dims, int heads, int dim, float eps,
+                                            int writes, int dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (rot_dims < 0 || rot_dims > rot || rot_dims % 2 != 0) return fail("latent_prepare: rotated dimensions must be even and at most the rotated part");
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t shared = (size_t)(rot_dims > 0 ? rot_dims : 1) * sizeof(float);
+    if (dtype == DT_F32)
+        latent_prepare_kernel<float><<<n_tokens, 128, shared, s>>>((float*)pages, q_eff, down, (const float*)q, ld_q, gain, inv_freq,
+                                                                   positions, token_item, block_table, max_blocks, page_size,
+                                                                   rank, rot, rot_dims, heads, dim, eps, writes);
+    else if (dtype == DT_BF16)
+        latent_prepare_kernel<bf16><<<n_tokens, 128, shared, s>>>((bf16*)pages, q_eff, down, (const bf16*)q, ld_q, gain, inv_freq,
+                                                                  positions, token_item, block_table, max_blocks, page_size,
+                                                                  rank, rot, rot_dims, heads, dim, eps, writes);
+    else
+        return fail("latent_prepare: unknown dtype");
+    return check_launch("latent_prepare_kernel");
+}
+
+// ---------------------------------------------------------------------------
+// A batch of products per head: out[t, head, n] = sum_k a[t, head, k] * w[head, n, k].
+// a: row stride lda, head stride a_head; out likewise; w [heads, N, K] contiguous.
+// The tile scheme of the plain linear kernel (64 x 64, fp32 FMA in order of k).
+// ---------------------------------------------------------------------------
+template <typename AT, typename WT, typename OT>
+__global__ void __launch_bounds__(256)
+head_linear_kernel(OT* __restrict__ out, const AT* __restrict__ a, const WT* __restrict__ w, int M, int N, int K, long lda,
+                   long ldo, long a_head, long o_head) {
+    constexpr int BM = 64, BN = 64, BK = 16;
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Ws[BK][BN + 4];
+    const int head = blockIdx.z;
+    a += (long)head * a_head;
+    out += (long)head * o_head;
+    w += (long)head * N * K;
+    int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += BK) {
+        for (int i = threadIdx.x; i < BM * BK; i += 256) {
+            int r = i / BK, c = i % BK;
+            int gm = m0 + r, gn = n0 + r, gk = k0 + c;
+            As[c][r] = (gm < M && gk < K) ? to_f32(a[(long)gm * lda + gk]) : 0.0f;
+            Ws[c][r] = (gn < N && gk < K) ? to_f32(w[(long)gn * K + gk]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; kk++) {
+            float av[4], wv[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) av[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; j++) wv[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        int gm = m0 + ty * 4 + i;
+        if (gm >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            int gn = n0 + tx * 4 + j;
+            if (gn < N) out[(long)gm * ldo + gn] = from_f32<OT>(acc[i][j]);
+        }
+    }
+}
+
+extern "C" int mllm_sequence_head_linear(void* out, const void* a, const void* w, int M, int N, int K, int heads, long lda,
+                                         long ldo, long a_head, long o_head, int a_dtype, int w_dtype, int out_dtype,
+                                         void* stream) {
+    if (M <= 0 || N <= 0 || heads <= 0) return 0;
+    if (K <= 0) return fail("head_linear: K must be positive");
+    if ((M + 63) / 64 > 65535 || heads > 65535) return fail("head_linear: too many rows or heads for one launch");
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid((N + 63) / 64, (M + 63) / 64, heads);
+#define MLLM_HEAD_LINEAR(AT, WT, OT)                                                                             \
+    head_linear_kernel<AT, WT, OT><<<grid, 256, 0, s>>>((OT*)out, (const AT*)a, (const WT*)w, M, N, K, lda, ldo, \
+                                                        a_head, o_head)
+    if (a_dtype == DT_F32 && w_dtype == DT_F32 && out_dtype == DT_F32) MLLM_HEAD_LINEAR(float, float, float);
+    else if (a_dtype == DT_BF16 && w_dtype == DT_BF16 && out_dtype == DT_F32) MLLM_HEAD_LINEAR(bf16, bf16, float);
+    else if (a_dtype == DT_F32 && w_dtype == DT_BF16 && out_dtype == DT_BF16) MLLM_HEAD_LINEAR(float, bf16, bf16);
+    else if (a_dtype == DT_BF16 && w_dtype == DT_BF16 && out_dtype == DT_BF16) MLLM_HEAD_LINEAR(bf16, bf16, bf16);
+    else return fail("head_linear: unsupported combination of element types");
+#undef MLLM_HEAD_LINEAR
+    return check_launch("head_linear_kernel");
+}
+
+// ---------------------------------------------------------------------------
+// Causal attention over a shared latent, one block per (token, head).
+// Every cached token is one row [rank + rot] of the pages; the score of query (t, head)
+// against it is q_eff[t, head, :] . row * scale, and the row's first `rank` entries are its
+// value.  The query at position p sees positions 0 .. p of its own request.  Four warps take
+// the keys in turn, each with an online softmax (32-bit); their states are merged in a fixed
+// order.  out[t, head, :rank] in 32-bit.  R: 32-element pieces of a row a lane may hold.
+// ---------------------------------------------------------------------------
+template <typename T, int R>
+__global__ void __launch_bounds__(128)
+latent_attention_kernel(float* __restrict__ out, const float* __restrict__ q_eff, const T* __restrict__ pages,
+                        const int* __restrict__ block_table, int max_blocks, const int* __restrict__ positions,
+                        const int* __restrict__ token_item, int heads, int rank, int rot, int page_size, float scale) {
+    const int t = blockIdx.x, h = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int p = positions[t];
+    const int* bt = block_table + (long)token_item[t] * max_blocks;
+    const int row_width = rank + rot;
+    const float* query = q_eff + ((long)t * heads + h) * row_width;
+    float qr[R], acc[R];
+#pragma unroll
+    for (int i = 0; i < R; i++) {
+        const int d = lane + 32 * i;
+        qr[i] = d < row_width ? query[d] : 0.0f;
+        acc[i] = 0.0f;
+    }
+    float m = -INFINITY, l = 0.0f;
+    for (int j = warp; j <= p; j += 4) {
+        const T* row = pages + ((long)bt[j / page_size] * page_size + (j % page_size)) * row_width;
+        float kv[R];
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < R; i++) {
+            const int d = lane + 32 * i;
+            kv[i] = d < row_width ? to_f32(row[d]) : 0.0f;
+            s = fmaf(qr[i], kv[i], s);
+        }
+        s = warp_sum(s) * scale;
+        const float m_new = fmaxf(m, s);
+        const float c = expf(m - m_new), e = expf(s - m_new);
+        l = l * c + e;
+#pragma unroll
+        for (int i = 0; i < R; i++) acc[i] = acc[i] * c + e * kv[i];       // (entries past `rank` are never stored)
+        m = m_new;
+    }
+    __shared__ float sm_m[4], sm_l[4];
+    __shared__ float sm_acc[4][R * 32];
+    if (lane == 0) {
+        sm_m[warp] = m;
+        sm_l[warp] = l;
+    }
+#pragma unroll
+    for (int i = 0; i < R; i++) sm_acc[warp][lane + 32 * i] = acc[i];
+    __syncthreads();
+    const float big = fmaxf(fmaxf(sm_m[0], sm_m[1]), fmaxf(sm_m[2], sm_m[3]));
+    float total = 0.0f, wgt[4];
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+        wgt[w] = sm_m[w] == -INFINITY ? 0.0f : expf(sm_m[w] - big);
+        total += sm_l[w] * wgt[w];
+    }
+    for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+        float o = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) o += sm_acc[w][d] * wgt[w];
+        out[((long)t * heads + h) * rank + d] = o / total;
+    }
+}
+
+template <typename T>
+static int launch_latent_attention(float* out, const float* q_eff, const void* pages, const int* block_table, int max_blocks,
+                                   const int* positions, const int* token_item, int n_tokens, int heads, int rank, int rot,
+                                   int page_size, float scale, cudaStream_t s) {
+    dim3 grid(n_tokens, heads);
+    const T* pg = (const T*)pages;
+    const int pieces = (rank + rot + 31) / 32;
+    if (pieces <= 4)
+        latent_attention_kernel<T, 4><<<grid, 128, 0, s>>>(out, q_eff, pg, block_table, max_blocks, positions, token_item, heads, rank, rot, page_size, scale);
+    else if (pieces <= 8)
+        latent_attention_kernel<T, 8><<<grid, 128, 0, s>>>(out, q_eff, pg, block_table, max_blocks, positions, token_item, heads, rank, rot, page_size, scale);
+    else if (pieces <= 20)
+        latent_attention_kernel<T, 20><<<grid, 128, 0, s>>>(out, q_eff, pg, block_table, max_blocks, positions, token_item, heads, rank, rot, page_size, scale);
+    else if (pieces <= 36)
+        latent_attention_kernel<T, 36><<<grid, 128, 0, s>>>(out, q_eff, pg, block_table, max_blocks, positions, token_item, heads, rank, rot, page_size, scale);
+    else
+        return fail("latent_attention: a cached row may hold at most 1152 entries");
+    return check_launch("latent_attention_kernel");
+}
+
+extern "C" int mllm_sequence_latent_attention(float* out, const float* q_eff, const void* pages, const int* block_table,
+                                              int max_blocks, const int* positions, const int* token_item, int n_tokens,
+                                              int heads, int rank, int rot, int page_size, float scale, int dtype,
+                                              void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (heads <= 0 || heads > 65535 || rank <= 0 || rot < 0) return fail("latent_attention: bad sizes");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == DT_F32)
+        return launch_latent_attention<float>(out, q_eff, pages, block_table, max_blocks, positions, token_item, n_tokens, heads,
+                                              rank, rot, page_size, scale, s);
+    if (dtype == DT_BF16)
+        return launch_latent_attention<bf16>(out, q_eff, pages, block_table, max_blocks, positions, token_item, n_tokens, heads,
+                                             rank, rot, page_size, scale, s);
+    return fail("latent_attention: unknown dtype");
+}
+
+// ---------------------------------------------------------------------------
+// Matrix memory, token by token.  Per (request, head): S [dim, vdim] with
+//   S <- a S + b k v^T,   o = S^T q
+// either with a fixed decay per head (a = decay[head], b = 1), or gated and stabilised:
+//   li = cap tanh((gi + bias_i) / cap),  lf = logsigmoid(cap tanh((gf + bias_f) / cap)),
+//   m' = max(lf + m, li),  a = exp(lf + m - m'),  b = exp(li - m'),
+//   n <- a n + b k,   o = S^T q / (max(|n . q|, exp(-m')) + 1e-6)
+// with m starting at 0.  q is multiplied by q_scale; with `silu`, q, k and v pass through
+// silu first.  State per slot: S [heads, dim, vdim], then (gated) n [heads, dim], m [heads],
+// all 32-bit, read at the start of the entry's tokens and written back at their end.
+// One block per (entry, head, slice of VS value columns); a thread owns one column of S in
+// shared memory and walks the entry's tokens in order; q and k of the next token are fetched
+// into the other half of a double buffer meanwhile.  Every slice keeps n and m for itself;
+// slice 0 writes them back.
+// ---------------------------------------------------------------------------
+struct MemoryScanParams {
+    float* out; long ld_out;                      // [T, heads * vdim], 32-bit
+    const void* q; const void* k; const void* v;  // rows of the activations' element type
+    long ld_q, ld_k, ld_v;
+    const float* gates; long ld_gates;            // [T, 2 * heads]: input gates, then forget gates (before bias); null: fixed decay
+    const float* gate_bias;                       // [2 * heads]
+    const float* decay;                           // [heads]
+    float* state; long state_stride;
+    const int* item_slot; const int* item_offset; const int* item_count;
+    int heads, dim, vdim;
+    float q_scale, gate_cap;
+    int silu, writes;
+};
+
+template <typename T, int VS>
+__global__ void __launch_bounds__(VS)
+memory_scan_kernel(MemoryScanParams p) {
+    extern __shared__ float shared[];
+    const int item = blockIdx.x, head = blockIdx.y, v0 = blockIdx.z * VS, tid = threadIdx.x;
+    const int count = p.item_count[item];
+    if (count <= 0) return;
+    const int dim = p.dim, vdim = p.vdim, heads = p.heads;
+    const bool gated = p.gates != nullptr;
+    const int column = v0 + tid;
+    const bool active = column < vdim;
+    float* S = shared;                       // [dim][VS]
+    float* nvec = S + (long)dim * VS;        // [dim]
+    float* qk = nvec + dim;                  // [2][2 * dim]: q then k
+    float* held = p.state + (long)p.item_slot[item] * p.state_stride;
+    float* S_held = held + (long)head * dim * vdim;
+    float* n_held = held + (long)heads * dim * vdim + (long)head * dim;
+    float* m_held = held + (long)heads * dim * vdim + (long)heads * dim + head;
+    for (int d = 0; d < dim; d++) S[d * VS + tid] = active ? S_held[(long)d * vdim + column] : 0.0f;
+    float m = 0.0f;
+    if (gated) {
+        for (int d = tid; d < dim; d += VS) nvec[d] = n_held[d];
+        m = *m_held;
+    }
+    const long first = p.item_offset[item];
+    const T* q = (const T*)p.q + (long)head * dim;
+    const T* k = (const T*)p.k + (long)head * dim;
+    const T* v = (const T*)p.v + (long)head * vdim;
+    auto fetch = [&](long row, float* into) {
+        for (int d = tid; d < dim; d += VS) {
+            float qd = to_f32(q[row * p.ld_q + d]), kd = to_f32(k[row * p.ld_k + d]);
+            if (p.silu) {
+                qd = silu_f(qd);
+                kd = silu_f(kd);
+            }
+            into[d] = qd * p.q_scale;
+            into[dim + d] = kd;
+        }
+    };
+    fetch(first, qk);
+    __syncthreads();
+    for (int i = 0; i < count; i++) {
+        const long row = first + i;
+        const float* qb = qk + (i & 1) * 2 * dim;
+        const float* kb = qb + dim;
+        float value = active ? to_f32(v[row * p.ld_v + column]) : 0.0f;
+        if (p.silu) value = silu_f(value);
+        float a, b, m_new = 0.0f;
+        if (gated) {
+            const float gi = p.gates[row * p.ld_gates + head] + p.gate_bias[head];
+            const float gf = p.gates[row * p.ld_gates + heads + head] + p.gate_bias[heads + head];
+            const float li = p.gate_cap * tanhf(gi / p.gate_cap);
+            const float lf = log_sigmoid_f(p.gate_cap * tanhf(gf / p.gate_cap));
+            m_new = fmaxf(lf + m, li);
+            a = expf(lf + m - m_new);
+            b = expf(li - m_new);
+        } else {
+            a = p.decay[head];
+            b = 1.0f;
+        }
+        float o = 0.0f, nq = 0.0f, kq = 0.0f;
+        const float bv = b * value;
+        for (int d = 0; d < dim; d++) {
+            const float qd = qb[d], kd = kb[d];
+            const float s = fmaf(a, S[d * VS + tid], kd * bv);
+            S[d * VS + tid] = s;
+            o = fmaf(s, qd, o);
+            if (gated) {
+                nq = fmaf(nvec[d], qd, nq);
+                kq = fmaf(kd, qd, kq);
+            }
+        }
+        if (gated) {
+            o /= fmaxf(fabsf(a * nq + b * kq), expf(-m_new)) + 1e-6f;
+            m = m_new;
+        }
+        if (active) p.out[row * p.ld_out + (long)head * vdim + column] = o;
+        __syncthreads();                     // every thread is done with nvec and with this token's q and k
+        if (gated)
+            for (int d = tid; d < dim; d += VS) nvec[d] = fmaf(a, nvec[d], b * kb[d]);
+        if (i + 1 < count) fetch(row + 1, qk + ((i + 1) & 1) * 2 * dim);
+        __syncthreads();
+    }
+    if (!p.writes) return;
+    if (active)
+        for (int d = 0; d < dim; d++) S_held[(long)d * vdim + column] = S[d * VS + tid];
+    if (gated && blockIdx.z == 0) {
+        for (int d = tid; d < dim; d += VS) n_held[d] = nvec[d];
+        if (tid == 0) *m_held = m;
+    }
+}
+
+extern "C" int mllm_sequence_memory_scan(const MemoryScanParams* params, int n_items, int dtype, void* stream) {
+    MemoryScanParams p = *params;
+    if (n_items <= 0) return 0;
+    if (p.heads <= 0 || p.heads > 65535 || p.dim <= 0 || p.vdim <= 0) return fail("memory_scan: bad sizes");
+    constexpr int VS = 32;
+    const size_t shared = ((size_t)p.dim * VS + 5 * (size_t)p.dim) * sizeof(float);
+    if (shared > 200 * 1024) return fail("memory_scan: the key size is too large for one slice of the state in shared memory");
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(n_items, p.heads, (p.vdim + VS - 1) / VS);
+    if (dtype == DT_F32) {
+        if (shared > 48 * 1024) cudaFuncSetAttribute(memory_scan_kernel<float, VS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        memory_scan_kernel<float, VS><<<grid, VS, shared, s>>>(p);
+    } else if (dtype == DT_BF16) {
+        if (shared > 48 * 1024) cudaFuncSetAttribute(memory_scan_kernel<bf16, VS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        memory_scan_kernel<bf16, VS><<<grid, VS, shared, s>>>(p);
+    } else {
+        return fail("memory_scan: unknown dtype");
+    }
+    return check_launch("memory_scan_kernel");
+}
+
+// ---------------------------------------------------------------------------
+// Weighted sum of all layer results.  kept[t, j, :] holds result j (j < index); the layer's
+// own result lies in `hidden`: it is stored as kept[t, index, :], and hidden becomes
+// sum_{j <= index} w[j] * kept[t, j, :] (with w null, hidden is only stored: the embedding output).
+// ---------------------------------------------------------------------------
+__global__ void depth_mix_kernel(float* __restrict__ hidden, float* __restrict__ kept, const float* __restrict__ w, int index,
+                                 int planes, int width, long n) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long t = i / width;
+    const int c = (int)(i % width);
+    float* mine = kept + (t * planes) * width + c;
+    const float x = hidden[i];
+    mine[(long)index * width] = x;
+    if (w == nullptr) return;
+    float acc = 0.0f;
+    for (int j = 0; j < index; j++) acc = fmaf(w[j], mine[(long)j * width], acc);
+    hidden[i] = fmaf(w[index], x, acc);
+}
+
+extern "C" int mllm_sequence_depth_mix(float* hidden, float* kept, const float* w, int index, int planes, int n_tokens,
+                                       int width, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (index < 0 || index >= planes) return fail("depth_mix: the result's index is outside the kept planes");
+    const long n = (long)n_tokens * width;
+    depth_mix_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(hidden, kept, w, index, planes, width, n);
+    return check_launch("depth_mix_kernel");
+}

@@ -84,6 +84,10 @@ class ControlBlock:
         for index, max_blocks in self.groups:
             offsets[("block_table", index)] = cursor
             cursor += n_items * max_blocks
+        # per entry: its slot, the row of its first token, its tokens, the position of its first token
+        for name in ("item_slot", "item_offset", "item_count", "item_start"):
+            offsets[name] = cursor
+            cursor += n_items
         return offsets, cursor
 
     def _ensure(self, size: int):
@@ -161,6 +165,8 @@ class ControlBlock:
             elif isinstance(name, tuple):
                 max_blocks = dict(self.groups)[name[1]]
                 views[name] = buffer[start:start + n_items * max_blocks].view(n_items, max_blocks)
+            elif name.startswith("item_"):
+                views[name] = buffer[start:start + n_items]
             else:
                 views[name] = buffer[start:start + n_tokens]
         return views
@@ -183,6 +189,8 @@ class StepContext:
         self.item_starts = []         # host: position of each entry's first token
         self.item_counts = []         # host: tokens of each entry
         self.item_offsets = []        # host: row of each entry's first token
+        self.item_slot = self.item_offset = self.item_count = self.item_start = None    # the same, on the device (int32)
+        self.kept_results = None      # fp32 [T, planes, width]: the embedding output and every layer's result, if the model keeps them
         self.decode_only = False      # every entry brings exactly one token
         self.fused = False            # the step goes to the one-kernel decode step
         self.dump = None              # a list: the model appends the residual stream after every run entry

@@ -315,6 +315,11 @@ class Engine:
             top_p = np.array([s.top_p for s in sampling], dtype=np.float32)
             seeds = np.array([s.seed & 0xFFFFFFFFFFFFFFFF for s in sampling], dtype=np.uint64)
             counters = np.array([s.counter for s in sampling], dtype=np.int32)
+        # the entries as the device sees them: slot, first row, rows, first position
+        item_slot = np.array(ctx.item_slots, dtype=np.int32)
+        item_offset = np.array(ctx.item_offsets, dtype=np.int32)
+        item_count = np.array(ctx.item_counts, dtype=np.int32)
+        item_start = np.array(ctx.item_starts, dtype=np.int32)
         n_real_want = n_want
         if (not decode_only and not dump_hidden and self.cuda_graphs and self.model.graph_safe
                 and n_want <= n_tokens and self._can_pad):
@@ -351,9 +356,17 @@ class Engine:
                 n_want = want_filled
             if tiles and extra:
                 tiles = tiles + [(n_items, n_tokens, 1, 0, 0, 1, 0, 1)] * (-len(tiles) % 4)
+            # the filler is one more entry, in the slot beyond the last request's (state of fixed
+            # size is kept there for nobody); the entries after it have no tokens
+            more = items_filled - n_items
+            item_slot = np.concatenate([item_slot, np.full(more, self.max_requests, dtype=np.int32)])
+            item_offset = np.concatenate([item_offset, np.full(more, n_tokens, dtype=np.int32)])
+            item_count = np.concatenate([item_count, np.array([extra] + [0] * (more - 1), dtype=np.int32)])
+            item_start = np.concatenate([item_start, np.zeros(more, dtype=np.int32)])
             n_tokens, n_items = filled, items_filled
         arrays = {"token_ids": token_ids, "positions": positions, "token_item": token_item, "want_rows": want_rows,
-                  "want_slots": want_slots, "att_tiles": np.array(tiles, dtype=np.int32)}
+                  "want_slots": want_slots, "att_tiles": np.array(tiles, dtype=np.int32), "item_slot": item_slot,
+                  "item_offset": item_offset, "item_count": item_count, "item_start": item_start}
         for index, table in tables.items():
             arrays[("block_table", index)] = table
         if sampling is not None:
@@ -377,9 +390,10 @@ class Engine:
         ctx.dump = [] if dump_hidden else None
         ctx.att_tiles, ctx.n_att_tiles = (views["att_tiles"] if tiles else None), len(tiles)
         ctx.n_split_tiles, ctx.att_parts, ctx.att_units = n_split, most_parts, units
-        for view in self.storage.views:
-            if view.kind == "paged":
-                view.block_table = views[("block_table", view.group)]
+        for view in self.storage.paged_views():
+            view.block_table = views[("block_table", view.group)]
+        ctx.item_slot, ctx.item_offset = views["item_slot"][:n_items], views["item_offset"][:n_items]
+        ctx.item_count, ctx.item_start = views["item_count"][:n_items], views["item_start"][:n_items]
 
         sample_views = None
         self._any_nucleus = sampling is not None and any(s.temperature > 0 and s.top_p < 1 for s in sampling)
@@ -460,7 +474,7 @@ class Engine:
         step in the same spirit, by keeping sampled tokens on the device
         (engine/src/gpt2_gpu_greedy.cu:80-119)."""
         if ctx.fused and self.fused is not None:
-            block_table = next(v.block_table for v in self.storage.views if v.kind == "paged")
+            block_table = next(v.block_table for v in self.storage.paged_views())
             try:
                 logits, self._sampled = self.fused.run(ctx, block_table, sample_views, self._any_nucleus)
                 self.step_kinds["one_kernel"] += 1

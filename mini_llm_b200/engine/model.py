@@ -20,6 +20,9 @@ class Model:
         self.spec = spec
         self.embedding = build_part(spec.embedding)
         self.position = build_part(spec.position) if spec.position is not None else None
+        self.embedding_norm = build_part(spec.embedding_norm) if spec.embedding_norm is not None else None
+        if self.embedding_norm is not None and not hasattr(self.embedding_norm, "normalize_in_place"):
+            raise ValueError(f"the norm '{spec.embedding_norm.kind}' cannot norm the embedded tokens in place")
         self.layers = []
         for layer in spec.layers:
             arrangement = get_arrangement(layer.arrangement)
@@ -44,21 +47,30 @@ class Model:
         found = [self.embedding]
         if self.position is not None:
             found.append(self.position)
+        if self.embedding_norm is not None:
+            found.append(self.embedding_norm)
         for _, parts in self.layers:
             found.extend(parts.values())
         found.extend([self.final_norm, self.head])
         return found
 
     def cache_needs(self):
-        """What each run entry keeps per request; None for an entry that reads another's cache."""
+        """What each run entry keeps per request: a need, or ``{role: need}`` when several parts of
+        the layer keep something; None for an entry that keeps nothing or reads another's cache."""
         needs = []
         for entry in self.spec.order:
             arrangement, parts = self.layers[entry.layer]
             if entry.cache_of is not None:
                 needs.append(None)
                 continue
-            need = parts[arrangement.mixer_role()].cache_need()
-            needs.append(None if isinstance(need, NoCache) else need)
+            mine = {role: parts[role].cache_need() for role in arrangement.cache_roles(parts)}
+            mine = {role: need for role, need in mine.items() if not isinstance(need, NoCache)}
+            if not mine:
+                needs.append(None)
+            elif tuple(arrangement.cache_roles(parts)) == (arrangement.mixer_role(),):
+                needs.append(mine[arrangement.mixer_role()])
+            else:
+                needs.append(mine)
         return needs
 
     def load(self, model_dir: str, dtype, device, runtime=None):
@@ -73,6 +85,14 @@ class Model:
     def forward(self, ctx, cache_views):
         """Run the step's tokens; returns fp32 logits [n_want, vocab] or None."""
         hidden = self.embedding.forward(ctx, self.position)
+        if self.embedding_norm is not None:
+            self.embedding_norm.normalize_in_place(ctx, hidden)
+        ctx.kept_results = None
+        if self.spec.keeps_layer_results:
+            # the embedding output is result 0; every layer's "depth_mix" part stores its own
+            ctx.kept_results = ctx.buffer("kept_results", (ctx.n_tokens, len(self.spec.order) + 1, self.spec.hidden_size),
+                                          hidden.dtype)
+            ctx.kernels.depth_mix(hidden, ctx.kept_results, None, 0)
         dump = getattr(ctx, "dump", None)
         if dump is not None:
             dump.append(hidden.clone())

@@ -41,6 +41,7 @@ LIBRARIES = {
     "gemm": "gemm_tcgen05.cu",
     "attention": "attention_tcgen05.cu",
     "fused": "fused_decode.cu",
+    "sequence": "sequence_kernels.cu",
 }
 
 _lock = threading.Lock()

@@ -91,6 +91,40 @@ class Kernels:
             return ops.layernorm_warp(out, x, gamma, beta, eps, rows)
         return ops.layernorm(out, x, gamma, beta, eps, rows)
 
+    # ---- norms in groups, short convolutions, latent attention, matrix memories, layer results ----
+    def grouped_rms_norm(self, out, x, gain, groups, eps, rows=None, gate=None, add=False):
+        self.launches += 1
+        return ops.grouped_rms_norm(out, x, gain, groups, eps, rows, gate, add)
+
+    def causal_taps(self, ctx, out, h, w, state, writes=True):
+        self.launches += 2 if writes and w.shape[1] > 1 else 1
+        return ops.causal_taps(out, h, w, state, ctx.positions, ctx.token_item, ctx.item_slot, ctx.item_start,
+                               ctx.item_offset, ctx.item_count, writes)
+
+    def latent_prepare(self, ctx, cache, q_eff, down, q, gain, inv_freq, rank, rot, rot_dims, heads, dim, eps):
+        self.launches += 1
+        return ops.latent_prepare(cache.k_pages, q_eff, down, q, gain, inv_freq, ctx.positions, ctx.token_item,
+                                  cache.block_table, cache.page_size, rank, rot, rot_dims, heads, dim, eps, cache.writes)
+
+    def head_linear(self, out, a, w, heads, a_head, o_head):
+        self.launches += 1
+        return ops.head_linear(out, a, w, heads, a_head, o_head)
+
+    def latent_attention(self, ctx, out, q_eff, cache, heads, rank, rot, scale):
+        self.launches += 1
+        self.chose("latent_attention", "latent_attention_plain", q_eff.shape[0], heads, rank + rot)
+        return ops.latent_attention_plain(out, q_eff, cache.k_pages, cache.block_table, ctx.positions, ctx.token_item,
+                                          heads, rank, rot, cache.page_size, scale)
+
+    def memory_scan(self, ctx, out, q, k, v, state, heads, dim, vdim, writes=True, **how):
+        self.launches += 1
+        return ops.memory_scan(out, q, k, v, state, ctx.item_slot, ctx.item_offset, ctx.item_count, heads, dim, vdim,
+                               writes=writes, **how)
+
+    def depth_mix(self, hidden, kept, weights, index):
+        self.launches += 1
+        return ops.depth_mix(hidden, kept, weights, index)
+
     def kv_store(self, k_pages, v_pages, k_src, v_src, positions, token_item, block_table, page_size):
         self.launches += 1
         return ops.kv_store(k_pages, v_pages, k_src, v_src, positions, token_item, block_table, page_size)
@@ -123,7 +157,9 @@ class Kernels:
         """out = epilogue(a @ w.T + bias).  ``a``: an activation tensor or a ``DeferredNorm``."""
         m, k = a.shape
         self.launches += 1
-        skinny = self._skinny(m, k, w.shape[0])
+        # activations the fast kernels do not apply, and products too narrow for a tile, go to the plain kernel
+        fast = epilogue in ops.GEMM_EPILOGUES and w.shape[0] >= 16
+        skinny = fast and self._skinny(m, k, w.shape[0])
         deferred = isinstance(a, DeferredNorm)
         if deferred and not (skinny and a.kind in self.FUSED_NORM_KINDS):
             a, deferred = a.materialize(ctx), False      # no kernel here norms this kind on the way in: the norm runs first
@@ -132,7 +168,7 @@ class Kernels:
             if deferred:
                 return ops.skinny_linear(out, a.x, w, bias, epilogue, norm=(a.gamma, a.beta, a.eps, a.rows))
             return ops.skinny_linear(out, a, w, bias, epilogue)
-        if not self.plain_only and ops.gemm_takes(a, w):
+        if fast and not self.plain_only and ops.gemm_takes(a, w):
             self.chose("linear", "gemm_tcgen05", m, w.shape[0], k)
             return ops.gemm_bf16(out, a, w, bias, epilogue, self.status(ctx.device))
         self.chose("linear", "linear_plain", m, w.shape[0], k)

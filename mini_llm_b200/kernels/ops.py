@@ -15,7 +15,8 @@ import torch
 from .lib import F, I, L, P, Function, KernelError, set_dependent_launch  # noqa: F401  (re-exported)
 
 DT_F32, DT_BF16 = 0, 1
-EPILOGUES = {"store": 0, "gelu_tanh": 1, "gelu_erf": 2, "add": 3}
+EPILOGUES = {"store": 0, "gelu_tanh": 1, "gelu_erf": 2, "add": 3, "relu_squared": 4, "silu": 5}
+GEMM_EPILOGUES = ("store", "gelu_tanh", "gelu_erf", "add")      # what the tensor-core and few-row kernels apply
 
 _DTYPE_CODE = {torch.float32: DT_F32, torch.bfloat16: DT_BF16}
 
@@ -779,3 +780,212 @@ def device_info() -> dict:
     _device_info(name, 256, values, ctypes.byref(memory))
     return {"name": name.value.decode(), "compute": f"{values[0]}.{values[1]}", "sms": values[2],
             "memory_bytes": memory.value, "runtime": values[3], "driver": values[4]}
+
+
+# ---- norms in groups, short convolutions, latent attention, matrix memories ----------------------
+
+_grouped_rms_norm = Function("sequence", "mllm_sequence_grouped_rms_norm",
+                             [P, L, P, L, P, P, P, L, I, I, I, F, I, I, I, P])
+
+
+def grouped_rms_norm(out, x, gain, groups, eps, rows=None, gate=None, add=False):
+    """Rows of the fp32 ``x`` [*, width], cut into ``groups`` equal consecutive pieces, each divided by
+    sqrt(mean(piece^2) + eps), the whole times ``gain``.  ``rows`` gathers input rows.  ``gate``
+    [R, width]: the result is also multiplied by sigmoid(gate).  ``add``: the fp32 ``out`` is added
+    to.  ``out`` may be ``x``."""
+    _check(out, "grouped_rms_norm.out", None, 2)
+    _check(x, "grouped_rms_norm.x", torch.float32, 2)
+    _check(gain, "grouped_rms_norm.gain", torch.float32, 1)
+    n_rows, width = out.shape
+    if x.shape[1] != width or gain.shape[0] != width or width % groups != 0:
+        raise KernelError(f"grouped_rms_norm: widths do not agree, or {width} is not a multiple of {groups} groups")
+    if rows is not None:
+        _check(rows, "grouped_rms_norm.rows", torch.int32, 1)
+        if rows.shape[0] < n_rows:
+            raise KernelError("grouped_rms_norm: fewer row indices than output rows")
+    elif x.shape[0] < n_rows:
+        raise KernelError("grouped_rms_norm: fewer input rows than output rows")
+    if gate is not None:
+        _check(gate, "grouped_rms_norm.gate", None, 2)
+        if gate.shape[0] < n_rows or gate.shape[1] != width:
+            raise KernelError("grouped_rms_norm: the gate has another shape")
+    if add and (out.dtype != torch.float32 or gate is not None):
+        raise KernelError("grouped_rms_norm: the residual sum is kept in 32-bit and takes no gate")
+    _grouped_rms_norm(out.data_ptr(), out.stride(0), x.data_ptr(), x.stride(0), gain.data_ptr(), _ptr(rows), _ptr(gate),
+                      gate.stride(0) if gate is not None else 0, n_rows, width, int(groups), float(eps), int(bool(add)),
+                      dtype_code(out.dtype), dtype_code(gate.dtype) if gate is not None else 0, _stream())
+    return out
+
+
+_causal_taps = Function("sequence", "mllm_sequence_causal_taps", [P, P, P, P, L, P, P, P, P, P, P, I, I, I, I, I, I, P])
+
+
+def causal_taps(out, h, w, state, positions, token_item, item_slot, item_start, item_offset, item_count, writes=True):
+    """out[t] = h[t] + sum_j w[:, j] * h[t - (taps - 1) + j] over the tokens of one request, per
+    channel; what lies before this step's portion comes from ``state`` [slots, taps - 1, width]
+    (fp32, oldest first), which is then moved on by this step's tokens (unless ``writes`` is false)."""
+    _check(out, "causal_taps.out", h.dtype, 2)
+    _check(h, "causal_taps.h", None, 2)
+    _check(w, "causal_taps.w", torch.float32, 2)
+    _check(state, "causal_taps.state", torch.float32, 3)
+    for name, t in (("positions", positions), ("token_item", token_item), ("item_slot", item_slot),
+                    ("item_start", item_start), ("item_offset", item_offset), ("item_count", item_count)):
+        _check(t, f"causal_taps.{name}", torch.int32, 1)
+    n, width = h.shape
+    taps = w.shape[1]
+    if not (out.is_contiguous() and h.is_contiguous() and w.is_contiguous()) or w.shape[0] != width or out.shape != h.shape:
+        raise KernelError("causal_taps: out, h and w must be contiguous and agree on the width")
+    if tuple(state.shape[1:]) != (max(taps - 1, 0), width) or (taps > 1 and state.stride(1) != width):
+        raise KernelError(f"causal_taps: the state must be [slots, {taps - 1}, {width}]")
+    _causal_taps(out.data_ptr(), h.data_ptr(), w.data_ptr(), state.data_ptr(), state.stride(0), positions.data_ptr(),
+                 token_item.data_ptr(), item_slot.data_ptr(), item_start.data_ptr(), item_offset.data_ptr(),
+                 item_count.data_ptr(), n, item_count.shape[0], width, taps, int(bool(writes)), dtype_code(h.dtype), _stream())
+    return out
+
+
+_latent_prepare = Function("sequence", "mllm_sequence_latent_prepare",
+                           [P, P, P, P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P])
+
+
+def latent_prepare(pages, q_eff, down, q, gain, inv_freq, positions, token_item, block_table, page_size, rank, rot,
+                   rot_dims, heads, dim, eps, writes=True):
+    """Per token: the first ``rank`` entries of the fp32 ``down`` row, normed by their root mean square
+    and times ``gain``, and its last ``rot`` entries with rotary positions, go into the token's row
+    of ``pages`` [n_pages, page_size, 1, rank + rot]; the rotated part of every head's query
+    (``q`` [T, heads * (dim + rot)]) gets rotary positions and goes to
+    ``q_eff`` [T, heads * (rank + rot)] (fp32), entries rank .. rank + rot of each head."""
+    _check(pages, "latent_prepare.pages", q.dtype)
+    _check(q_eff, "latent_prepare.q_eff", torch.float32, 2)
+    _check(down, "latent_prepare.down", torch.float32, 2)
+    _check(q, "latent_prepare.q", None, 2)
+    _check(gain, "latent_prepare.gain", torch.float32, 1)
+    _check(inv_freq, "latent_prepare.inv_freq", torch.float64, 1)
+    _check(block_table, "latent_prepare.block_table", torch.int32, 2)
+    n = q.shape[0]
+    row = rank + rot
+    if (not down.is_contiguous() or down.shape[1] != row or not q_eff.is_contiguous() or q_eff.shape[1] != heads * row
+            or q.shape[1] != heads * (dim + rot) or gain.shape[0] != rank or inv_freq.shape[0] < rot_dims // 2):
+        raise KernelError("latent_prepare: sizes do not agree")
+    if not pages.is_contiguous() or pages.numel() % (page_size * row) != 0 or not block_table.is_contiguous():
+        raise KernelError("latent_prepare: the pages do not hold whole pages of rows of rank + rot")
+    _latent_prepare(pages.data_ptr(), q_eff.data_ptr(), down.data_ptr(), q.data_ptr(), q.stride(0), gain.data_ptr(),
+                    inv_freq.data_ptr(), positions.data_ptr(), token_item.data_ptr(), block_table.data_ptr(),
+                    block_table.shape[1], page_size, n, rank, rot, rot_dims, heads, dim, float(eps), int(bool(writes)),
+                    dtype_code(q.dtype), _stream())
+
+
+_head_linear = Function("sequence", "mllm_sequence_head_linear", [P, P, P, I, I, I, I, L, L, L, L, I, I, I, P])
+
+
+def head_linear(out, a, w, heads, a_head, o_head):
+    """out[t, head, :] = w[head] @ a[t, head, :] for every head: ``w`` [heads, N, K]; head ``h`` of
+    ``a`` starts at column ``h * a_head`` (K entries), of ``out`` at ``h * o_head`` (N entries)."""
+    _check(out, "head_linear.out", None, 2)
+    _check(a, "head_linear.a", None, 2)
+    _check(w, "head_linear.w", None, 3)
+    m = a.shape[0]
+    n, k = w.shape[1], w.shape[2]
+    if (w.shape[0] != heads or not w.is_contiguous() or out.shape[0] != m or (heads - 1) * a_head + k > a.shape[1]
+            or (heads - 1) * o_head + n > out.shape[1]):
+        raise KernelError("head_linear: shapes do not agree")
+    _head_linear(out.data_ptr(), a.data_ptr(), w.data_ptr(), m, n, k, heads, a.stride(0), out.stride(0), a_head, o_head,
+                 dtype_code(a.dtype), dtype_code(w.dtype), dtype_code(out.dtype), _stream())
+    return out
+
+
+_latent_attention = Function("sequence", "mllm_sequence_latent_attention", [P, P, P, P, I, P, P, I, I, I, I, I, F, I, P])
+
+
+def latent_attention_plain(out, q_eff, pages, block_table, positions, token_item, heads, rank, rot, page_size, scale):
+    """Causal attention of every token of the step over its request's cached rows [rank + rot]:
+    score = q_eff[t, head] . row * scale, value = the row's first ``rank`` entries;
+    out [T, heads * rank] in 32-bit."""
+    _check(out, "latent_attention.out", torch.float32, 2)
+    _check(q_eff, "latent_attention.q_eff", torch.float32, 2)
+    _check(pages, "latent_attention.pages")
+    _check(block_table, "latent_attention.block_table", torch.int32, 2)
+    n = q_eff.shape[0]
+    if (not out.is_contiguous() or not q_eff.is_contiguous() or out.shape != (n, heads * rank)
+            or q_eff.shape[1] != heads * (rank + rot) or not pages.is_contiguous() or not block_table.is_contiguous()):
+        raise KernelError("latent_attention: sizes do not agree")
+    _latent_attention(out.data_ptr(), q_eff.data_ptr(), pages.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+                      positions.data_ptr(), token_item.data_ptr(), n, heads, rank, rot, page_size, float(scale),
+                      dtype_code(pages.dtype), _stream())
+    return out
+
+
+class _MemoryScanParams(ctypes.Structure):
+    _fields_ = [("out", P), ("ld_out", L), ("q", P), ("k", P), ("v", P), ("ld_q", L), ("ld_k", L), ("ld_v", L),
+                ("gates", P), ("ld_gates", L), ("gate_bias", P), ("decay", P), ("state", P), ("state_stride", L),
+                ("item_slot", P), ("item_offset", P), ("item_count", P), ("heads", I), ("dim", I), ("vdim", I),
+                ("q_scale", F), ("gate_cap", F), ("silu", I), ("writes", I)]
+
+
+_memory_scan = Function("sequence", "mllm_sequence_memory_scan", [ctypes.POINTER(_MemoryScanParams), I, I, P])
+
+
+def memory_state_floats(heads, dim, vdim, gated) -> int:
+    """Floats of a request's matrix-memory state: S [heads, dim, vdim], and, gated, n [heads, dim]
+    and m [heads]."""
+    return heads * dim * vdim + (heads * dim + heads if gated else 0)
+
+
+def memory_scan(out, q, k, v, state, item_slot, item_offset, item_count, heads, dim, vdim, q_scale=1.0, silu=False,
+                gates=None, gate_bias=None, gate_cap=0.0, decay=None, writes=True):
+    """The matrix-memory recurrence over each entry's tokens, in order:
+    S <- a S + b k v^T, out = S^T q, with a fixed decay per head (``decay`` [heads]; a = decay,
+    b = 1) or with ``gates`` [T, 2 * heads] (fp32: input gates then forget gates, ``gate_bias``
+    added): capped, exponential, stabilised by a running maximum, the output divided by
+    max(|n . q|, exp(-m)) + 1e-6.  q, k [T, heads * dim], v [T, heads * vdim] (any row stride);
+    out fp32 [T, heads * vdim]; ``state`` fp32 [slots, memory_state_floats(...)]."""
+    _check(out, "memory_scan.out", torch.float32, 2)
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _check(t, f"memory_scan.{name}", q.dtype, 2)
+    _check(state, "memory_scan.state", torch.float32, 2)
+    n = q.shape[0]
+    gated = gates is not None
+    if (q.shape[1] != heads * dim or k.shape[1] != heads * dim or v.shape[1] != heads * vdim
+            or out.shape != (n, heads * vdim) or state.shape[1] != memory_state_floats(heads, dim, vdim, gated)
+            or state.stride(1) != 1):
+        raise KernelError("memory_scan: sizes do not agree")
+    params = _MemoryScanParams()
+    params.out, params.ld_out = out.data_ptr(), out.stride(0)
+    params.q, params.k, params.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    params.ld_q, params.ld_k, params.ld_v = q.stride(0), k.stride(0), v.stride(0)
+    if gated:
+        _check(gates, "memory_scan.gates", torch.float32, 2)
+        _check(gate_bias, "memory_scan.gate_bias", torch.float32, 1)
+        if gates.shape[1] != 2 * heads or gate_bias.shape[0] != 2 * heads or gate_cap <= 0:
+            raise KernelError("memory_scan: gates are [T, 2 * heads] with a positive cap")
+        params.gates, params.ld_gates, params.gate_bias = gates.data_ptr(), gates.stride(0), gate_bias.data_ptr()
+    else:
+        _check(decay, "memory_scan.decay", torch.float32, 1)
+        if decay.shape[0] != heads:
+            raise KernelError("memory_scan: one decay per head")
+        params.decay = decay.data_ptr()
+    params.state, params.state_stride = state.data_ptr(), state.stride(0)
+    params.item_slot, params.item_offset, params.item_count = item_slot.data_ptr(), item_offset.data_ptr(), item_count.data_ptr()
+    params.heads, params.dim, params.vdim = heads, dim, vdim
+    params.q_scale, params.gate_cap = float(q_scale), float(gate_cap)
+    params.silu, params.writes = int(bool(silu)), int(bool(writes))
+    _memory_scan(ctypes.byref(params), item_count.shape[0], dtype_code(q.dtype), _stream())
+    return out
+
+
+_depth_mix = Function("sequence", "mllm_sequence_depth_mix", [P, P, P, I, I, I, I, P])
+
+
+def depth_mix(hidden, kept, weights, index):
+    """kept[:, index] = hidden; then, with ``weights`` [index + 1] (fp32), hidden = sum over
+    j <= index of weights[j] * kept[:, j].  kept: fp32 [T, planes, width]."""
+    _check(hidden, "depth_mix.hidden", torch.float32, 2)
+    _check(kept, "depth_mix.kept", torch.float32, 3)
+    n, width = hidden.shape
+    if not hidden.is_contiguous() or not kept.is_contiguous() or kept.shape[0] != n or kept.shape[2] != width:
+        raise KernelError("depth_mix: hidden [T, width] and kept [T, planes, width] must be contiguous")
+    if weights is not None:
+        _check(weights, "depth_mix.weights", torch.float32, 1)
+        if weights.shape[0] != index + 1:
+            raise KernelError(f"depth_mix: {weights.shape[0]} weights for {index + 1} results")
+    _depth_mix(hidden.data_ptr(), kept.data_ptr(), _ptr(weights), index, kept.shape[1], n, width, _stream())
+    return hidden

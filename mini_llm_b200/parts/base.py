@@ -16,8 +16,14 @@ residual stream [T, width]; "act" tensors have the engine's element type):
     place.  ``cache`` is this run entry's ``cache.views.LayerCache``; when
     ``cache.writes`` is false the entry reads another entry's cache and must
     not store into it.
+``Mixer.compute(ctx, x, cache) -> fp32 [T, width]``  (optional)
+    the mixer's output itself, for arrangements that norm it before the sum.
 ``FeedForward.forward(ctx, x, hidden)``
     add the feed-forward output for ``x`` into ``hidden`` in place.
+``FeedForward.compute(ctx, x) -> fp32 [T, width]``  (optional)
+``InputFilter.forward(ctx, x, cache) -> act [T, width]``
+    what a mixer reads instead of ``x`` (a short convolution over time, for instance);
+    ``cache_need()`` as for a mixer: the filter's own state per request.
 ``PositionEncoding.add_to_hidden(ctx, hidden)``
     for encodings that act on the embedded tokens; ``additive_table()`` may
     return the table so that the embedding gather fuses the sum.  Encodings
@@ -80,6 +86,14 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class InputFilter(Part):
+    def cache_need(self):
+        return NoCache()
+
+    def forward(self, ctx, x, cache):
+        raise NotImplementedError
+
+
 class PositionEncoding(Part):
     def add_to_hidden(self, ctx, hidden):
         raise NotImplementedError
@@ -108,6 +122,11 @@ class Arrangement:
 
     def mixer_role(self) -> str:
         return "mixer"
+
+    def cache_roles(self, parts: dict) -> tuple:
+        """The roles whose parts keep something per request.  With more than one, ``run``
+        gets a cache with one view per role (``cache.of(role)``)."""
+        return (self.mixer_role(),)
 
 
 _PART_KINDS: dict[str, type] = {}

@@ -3,6 +3,13 @@
 "pre_norm" is the reference's block (engine/src/transformer_block.c:49-71):
 ``r = x + mixer(norm_1(x))``, then ``out = r + feed_forward(norm_2(r))``.  The
 residual stream stays 32-bit; mixers and feed-forwards add into it in place.
+
+"sandwich_norm" norms every sublayer on both sides:
+``x <- x + norm_1b(mixer(filter(norm_1(x))))``, then, if the layer has a feed-forward,
+``x <- x + norm_2b(feed_forward(norm_2(x)))``, then, if it has one, its "depth_mix" part replaces
+x by a weighted sum of all layer results so far.  The input filter (a short convolution, say) and
+the feed-forward are optional roles; the mixer and the feed-forward hand over their output itself
+(``compute``), and the outer norm adds it onto the stream (``add_normed``).
 """
 
 from __future__ import annotations
@@ -28,4 +35,26 @@ class PreNorm(Arrangement):
         parts["feed_forward"].forward(ctx, x, hidden)
 
 
+class SandwichNorm(Arrangement):
+    roles = ("norm_1", "mixer", "norm_1b")
+    optional_roles = ("input_filter", "norm_2", "feed_forward", "norm_2b", "depth_mix")
+
+    def cache_roles(self, parts):
+        return tuple(role for role in ("mixer", "input_filter") if role in parts)
+
+    def run(self, ctx, parts, hidden, cache):
+        composite = getattr(cache, "kind", "none") == "composite"
+        x = parts["norm_1"].forward(ctx, hidden, tag="norm_1")
+        if "input_filter" in parts:
+            x = parts["input_filter"].forward(ctx, x, cache.of("input_filter") if composite else cache)
+        y = parts["mixer"].compute(ctx, x, cache.of("mixer") if composite else cache)
+        parts["norm_1b"].add_normed(ctx, hidden, y)
+        if "feed_forward" in parts:
+            x = parts["norm_2"].forward(ctx, hidden, tag="norm_2")
+            parts["norm_2b"].add_normed(ctx, hidden, parts["feed_forward"].compute(ctx, x))
+        if "depth_mix" in parts:
+            parts["depth_mix"].forward(ctx, hidden)
+
+
 register_arrangement("pre_norm", PreNorm())
+register_arrangement("sandwich_norm", SandwichNorm())

@@ -1,6 +1,12 @@
 """Layer norm: mean, biased variance of the centred values, then
 ``(x - mean) / sqrt(var + eps) * gain + shift`` (engine/src/layernorm.c:12-33).
-Statistics are 32-bit; the output has the engine's element type."""
+Statistics are 32-bit; the output has the engine's element type.
+
+Norm by root mean square in groups (``grouped_rms_norm``): the row is cut into ``groups`` equal
+consecutive pieces, each divided by ``sqrt(mean(piece^2) + eps)``, and the whole multiplied by one
+gain vector; ``groups=1`` is the plain RMS norm.  Besides the interface of every norm it can norm
+the residual stream in place and add a normed sublayer result onto it, which is what an
+arrangement with norms on both sides of a sublayer needs."""
 
 from __future__ import annotations
 
@@ -36,4 +42,34 @@ class LayerNorm(Norm):
         return out
 
 
+class GroupedRmsNorm(Norm):
+    graph_safe = True
+
+    def __init__(self, prefix, width: int, eps: float, groups: int = 1, name: str = "weight"):
+        super().__init__(prefix)
+        self.width, self.eps, self.groups, self.name = int(width), float(eps), int(groups), name
+        if self.groups <= 0 or self.width % self.groups != 0:
+            raise ValueError(f"{self.full_name(name)}: a width of {self.width} does not split into {self.groups} equal groups")
+
+    def weight_specs(self):
+        return [WeightSpec(self.full_name(self.name), (self.width,), role="vector", init="gain")]
+
+    def forward(self, ctx, x, rows=None, tag="norm"):
+        n_rows = x.shape[0] if rows is None else rows.shape[0]
+        out = ctx.buffer(tag, (n_rows, self.width), ctx.act_dtype)
+        ctx.kernels.grouped_rms_norm(out, x, self.w(self.name), self.groups, self.eps, rows)
+        return out
+
+    def normalize_in_place(self, ctx, hidden):
+        """The fp32 stream itself is normed (after an embedding, for instance)."""
+        ctx.kernels.grouped_rms_norm(hidden, hidden, self.w(self.name), self.groups, self.eps)
+        return hidden
+
+    def add_normed(self, ctx, hidden, y):
+        """hidden += norm(y): a sublayer's fp32 result is normed on its way onto the stream."""
+        ctx.kernels.grouped_rms_norm(hidden, y, self.w(self.name), self.groups, self.eps, add=True)
+        return hidden
+
+
 register_part("layer_norm", LayerNorm)
+register_part("grouped_rms_norm", GroupedRmsNorm)

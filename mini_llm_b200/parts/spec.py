@@ -85,6 +85,9 @@ class ModelSpec:
     order: tuple                       # of RunEntry
     final_norm: PartSpec
     head: PartSpec
+    embedding_norm: PartSpec | None = None   # a norm applied to the embedded tokens, in place, before the first layer
+    keeps_layer_results: bool = False  # the embedding output and every run entry's result stay at hand for the
+                                       # layers' "depth_mix" parts (a weighted sum over all of them)
     file_prefixes: tuple = ("",)       # prefixes a weights file may put before every name
     ignored_weights: tuple = ()        # regular expressions of file names that are no parameters
     eos_token_id: int | None = None
@@ -104,11 +107,14 @@ class ModelSpec:
 
 @dataclass(frozen=True)
 class PagedKV:
-    """Keys and values of every cached token (or of the last ``window`` tokens), in pages."""
+    """Keys and values of every cached token (or of the last ``window`` tokens), in pages.
+    With ``has_values`` false only one row per token is kept (the ``keys``): a mixer whose values
+    are a part of that row (attention over a shared latent) needs no second pool."""
 
     n_kv_heads: int
     head_size: int
     window: int | None = None          # None: all keys
+    has_values: bool = True
 
 
 @dataclass(frozen=True)

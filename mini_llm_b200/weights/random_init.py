@@ -38,6 +38,8 @@ def model_parts(spec):
     parts = [build_part(spec.embedding)]
     if spec.position is not None:
         parts.append(build_part(spec.position))
+    if spec.embedding_norm is not None:
+        parts.append(build_part(spec.embedding_norm))
     for layer in spec.layers:
         parts.extend(build_part(p) for p in layer.parts.values())
     parts.append(build_part(spec.final_norm))
