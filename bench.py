@@ -64,6 +64,9 @@ def parse_args():
     parser.add_argument("--kernels", action="store_true",
                         help="time single kernels (matrix products at forced tile widths, prompt attention) back to "
                              "back in a replayed graph and print one line each: the tables of profiles/ come from this")
+    parser.add_argument("--compare", default=None, choices=("fuvolix",),
+                        help="prefill and decode of Fuvolix stacks at sizes of real layers (random weights), beside GPT-2 "
+                             "of equal width, depth and inner size, and their mixers' kernels alone; one line each")
     parser.add_argument("--tokens-out", default=None,
                         help="(--impl reference) write the greedy tokens of the fixed check workload to this file "
                              "and print nothing else")
@@ -744,6 +747,177 @@ def run_kernels():
     return 0
 
 
+# Fuvolix stacks beside GPT-2 of equal width, depth and inner size: layers in threes (attention over a
+# latent with a feed-forward, a gated matrix memory, a decaying matrix memory with a feed-forward).
+FUVOLIX_SIZES = {
+    "small": {"width": 768, "layers": 12, "ff": 3072, "gpt2": "small",
+              "latent": {"heads": 12, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 256},
+              "mlstm": {"heads": 4, "dim": 96, "vdim": 192}, "lightning": {"heads": 12, "dim": 64, "vdim": 64}},
+    "medium": {"width": 1024, "layers": 24, "ff": 4096, "gpt2": "medium",
+               "latent": {"heads": 16, "dim": 64, "rot_dim": 64, "vdim": 64, "kv_rank": 512},
+               "mlstm": {"heads": 4, "dim": 128, "vdim": 256}, "lightning": {"heads": 16, "dim": 64, "vdim": 64}},
+}
+FP32_FMA_TFLOPS_NOMINAL = 148 * 128 * 2 * 1.965e9 / 1e12      # 32-bit FMA of 148 SMs at the highest clock: no measured figure exists
+
+
+def fuvolix_config(size: dict, vocab: int) -> dict:
+    lat, mem, lit = size["latent"], size["mlstm"], size["lightning"]
+    three = [
+        {"type": "latent_attention", "mlp": {"kind": "dense", "ff": size["ff"]},
+         "mixer": dict(lat, scale=(lat["dim"] + lat["rot_dim"]) ** -0.5, rot={"base": 10000.0, "dims": lat["rot_dim"]})},
+        {"type": "mlstm", "mlp": None, "mixer": dict(mem, gate_cap=15.0)},
+        {"type": "lightning", "mlp": {"kind": "dense", "ff": size["ff"]},
+         "mixer": dict(lit, decay=[1.0 - 2.0 ** -(2 + 6 * h / max(lit["heads"] - 1, 1)) for h in range(lit["heads"])])},
+    ]
+    return {"architecture": "Fuvolix", "vocab": vocab, "width": size["width"], "norm": {"eps": 1e-5, "groups": 4},
+            "canon": {"taps": 4}, "layers": [three[i % 3] for i in range(size["layers"])]}
+
+
+def mixer_kernels(torch, size: dict, peak: dict):
+    """The mixers' kernels alone, replayed back to back on operands of their own: prompt portions
+    (2 x 1,024 tokens) and single tokens (8 requests at 1,023 cached tokens), each with the work it
+    must do and the fraction of its bound: 32-bit FMA (nominal) where the sums are 32-bit by the
+    design's rule, measured HBM copy bandwidth where the state or the cache is streamed."""
+    from mini_llm_b200.kernels import ops
+    lines = []
+    page, fma_peak = 64, FP32_FMA_TFLOPS_NOMINAL
+    dev = lambda values: torch.tensor(values, dtype=torch.int32, device="cuda")
+
+    def add(kernel, us, flops=None, bytes_moved=None, **more):
+        line = {"kernel": kernel, "us": round(us, 2), **more}
+        if flops is not None:
+            line.update(tflops=round(flops / us / 1e6, 2), frac_fp32_fma_nominal=round(flops / us / 1e6 / fma_peak, 3))
+        if bytes_moved is not None:
+            line.update(gbs=round(bytes_moved / us / 1e3, 1), frac_hbm_measured=round(bytes_moved / us / 1e3 / peak["hbm_gbs"], 3))
+        lines.append(line)
+
+    # ---- attention over the latent, beside GPT-2's attention of as many heads of 64 ----
+    lat = size["latent"]
+    heads, rank, rot = lat["heads"], lat["kv_rank"], lat["rot_dim"]
+    row = rank + rot
+    for name, lengths, new in (("prompts, 2 x 1024", [1024, 1024], [1024, 1024]), ("single tokens, 8 x 1024", [1024] * 8, [1] * 8)):
+        blocks = [-(-n // page) for n in lengths]
+        table = torch.zeros(len(lengths), max(blocks), dtype=torch.int32)
+        at = 0
+        for i, count in enumerate(blocks):
+            table[i, :count] = torch.arange(at, at + count, dtype=torch.int32)
+            at += count
+        table = table.cuda()
+        n = sum(new)
+        offsets = [sum(new[:i]) for i in range(len(new))]
+        starts = [length - count for length, count in zip(lengths, new)]
+        positions = torch.cat([torch.arange(s, s + m) for s, m in zip(starts, new)]).int().cuda()
+        token_item = torch.cat([torch.full((m,), i) for i, m in enumerate(new)]).int().cuda()
+        pairs = sum(sum(range(s + 1, s + m + 1)) for s, m in zip(starts, new)) * heads         # (query row, key) pairs
+        pages = [torch.randn(sum(blocks) + 1, page, 1, row, device="cuda").bfloat16() for _ in range(4)]
+        q_eff = torch.randn(n, heads * row, device="cuda")
+        out = torch.empty(n, heads * rank, device="cuda")
+        if len(new) == 2:
+            tiles, _, _ = ops.attention_tiles(offsets, new, starts, split=False)
+            tiles_d = dev(tiles)
+            us = replayed_us(torch, lambda i: ops.latent_attention_tiled(out, q_eff, pages[i % 4], table, positions, token_item, heads,
+                                                                         rank, rot, page, 0.1, tiles=tiles_d, n_tiles=len(tiles)))
+            add(f"latent attention in tiles, {name}", us, flops=2.0 * pairs * (row + rank), heads=heads, row=row)
+        else:
+            reach = table.shape[1] * page
+            parts = max(1, min(32, 296 // (n * -(-heads // 32)), reach // 64))
+            per_part = -(-(-(-reach // parts)) // 32) * 32
+            scratch = (torch.empty(n * heads * parts * rank, device="cuda"), torch.empty(n * heads * parts * 2, device="cuda"))
+            us = replayed_us(torch, lambda i: ops.latent_attention_tiled(out, q_eff, pages[i % 4], table, positions, token_item, heads,
+                                                                         rank, rot, page, 0.1, parts=parts, keys_per_part=per_part,
+                                                                         scratch=scratch))
+            add(f"latent attention in parts, {name}", us, bytes_moved=sum(lengths) * row * 2.0, heads=heads, row=row, parts=parts)
+        # GPT-2's kernels at as many heads of 64
+        head = 64
+        k_pages = [torch.randn(sum(blocks) + 1, page, heads, head, device="cuda").bfloat16() for _ in range(4)]
+        v_pages = [torch.randn(sum(blocks) + 1, page, heads, head, device="cuda").bfloat16() for _ in range(4)]
+        q = torch.randn(n, heads * head, device="cuda").bfloat16()
+        o = torch.empty_like(q)
+        status, work = torch.zeros(1, dtype=torch.int32, device="cuda"), torch.zeros(2, dtype=torch.int32, device="cuda")
+        if len(new) == 2:
+            units, n_split, most = ops.attention_units(offsets, new, starts, heads, torch.cuda.get_device_properties(0).multi_processor_count)
+            units_d = dev(units)
+            scratch = None
+            if n_split:
+                scratch = (torch.empty(n_split * heads * most * ops.ATTENTION_UNIT * (head + 4), device="cuda"),
+                           torch.zeros(2 * n_split * heads, dtype=torch.int32, device="cuda"))
+            us = replayed_us(torch, lambda i: ops.attention_prefill_two_tiles(o, q, k_pages[i % 4], v_pages[i % 4], table, units_d, len(units),
+                                                                              heads, heads, head, page, 0.125, 0, status, work, scratch,
+                                                                              n_split, most))
+            flops = 2.0 * pairs * 2 * head
+            lines.append({"kernel": f"GPT-2 attention (tensor cores), {name}", "us": round(us, 2), "tflops": round(flops / us / 1e6, 2),
+                          "frac_bf16_measured": round(flops / us / 1e6 / peak["bf16_tflops"], 3), "heads": heads})
+        else:
+            chunk, reach = 128, table.shape[1] * page
+            acc = torch.empty(64 * heads * (reach // 64) * head, device="cuda")
+            ml = torch.empty(64 * heads * (reach // 64) * 2, device="cuda")
+            counters = torch.zeros(64 * heads, dtype=torch.int32, device="cuda")
+            us = replayed_us(torch, lambda i: ops.split_attention(o, q, k_pages[i % 4], v_pages[i % 4], table, positions, token_item, heads,
+                                                                  heads, head, page, 0.125, 0, chunk, -(-reach // chunk), acc, ml, counters))
+            add(f"GPT-2 attention over split keys, {name}", us, bytes_moved=sum(lengths) * heads * head * 2 * 2.0, heads=heads)
+    # ---- the matrix memories ----
+    for kind in ("mlstm", "lightning"):
+        mem = size[kind]
+        h, dim, vdim = mem["heads"], mem["dim"], mem["vdim"]
+        gated = kind == "mlstm"
+        floats = ops.memory_state_floats(h, dim, vdim, gated)
+        for name, counts, chunked in (("prompts, 2 x 1024", [1024, 1024], True), ("single tokens, 8", [1] * 8, False)):
+            n = sum(counts)
+            projected = [torch.randn(n, 2 * h * dim + h * vdim, device="cuda").bfloat16() for _ in range(4)]
+            states = [torch.zeros(len(counts), floats, device="cuda") for _ in range(4)]
+            out = torch.empty(n, h * vdim, device="cuda")
+            how = (dict(gates=torch.randn(n, 2 * h, device="cuda"), gate_bias=torch.zeros(2 * h, device="cuda"), gate_cap=15.0,
+                        q_scale=dim ** -0.5) if gated else dict(decay=torch.full((h,), 0.98, device="cuda"), silu=True))
+            slots, offs = dev(list(range(len(counts)))), dev([sum(counts[:i]) for i in range(len(counts))])
+            cnts = dev(counts)
+
+            def launch(i):
+                x = projected[i % 4]
+                ops.memory_scan(out, x[:, :h * dim], x[:, h * dim:2 * h * dim], x[:, 2 * h * dim:], states[i % 4], slots, offs, cnts,
+                                h, dim, vdim, chunked=chunked, **how)
+            us = replayed_us(torch, launch)
+            if chunked:
+                # per chunk of 32 tokens and head: 32 x 32 x dim scores (once per slice of 32 value columns),
+                # 32 x vdim x (dim + 32 / 2) for the outputs, dim x vdim x 32 for the state
+                slices = -(-vdim // 32)
+                per_chunk = slices * 32 * 32 * dim + 32 * vdim * (dim + 16) + dim * vdim * 32
+                add(f"{kind} memory, 32 tokens at a time, {name}", us, flops=2.0 * per_chunk * (n // 32) * h, heads=h, dim=dim, vdim=vdim)
+            else:
+                add(f"{kind} memory, token by token, {name}", us, bytes_moved=2.0 * len(counts) * floats * 4, heads=h, dim=dim, vdim=vdim)
+    return lines
+
+
+def run_compare(args):
+    """Fuvolix beside GPT-2 of equal width, depth and inner size: the prompt step of 2,048 tokens
+    (2 x 1,024) and the decode step of ``--batch`` requests at a context of 1,024, in bfloat16,
+    through ``Engine.step``; then the mixers' kernels alone.  One JSON line per measurement."""
+    import torch
+    from mini_llm_b200.config import config_from_dict
+    from mini_llm_b200.engine import Engine
+    from mini_llm_b200.weights import write_random_model
+    peak = peaks()
+    context, vocab = 1024, GPT2_SMALL["vocab_size"]
+    for name, size in FUVOLIX_SIZES.items():
+        for design in ("fuvolix", "gpt2"):
+            raw = fuvolix_config(size, vocab) if design == "fuvolix" else dict(GPT2_SMALL, **SIZES[size["gpt2"]])
+            with tempfile.TemporaryDirectory() as folder:
+                write_random_model(config_from_dict(raw), 0, folder, recipe="gpt2", store_dtype="bfloat16")
+                engine = Engine(folder, dtype="bfloat16", max_requests=16, cache_tokens=16 * context, max_tokens_per_step=2048,
+                                **({"page_size": args.page_size} if args.page_size else {}))
+                prefill_ms = prefill_run(engine, 2, 1024, vocab)
+                decode_ms, launches, _ = decode_run(engine, args.batch, args.steps, args.warmup, context, vocab)
+                print(json.dumps({"design": design, "size": name, "width": size["width"], "layers": size["layers"], "inner": size["ff"],
+                                  "prefill_2048_tokens_ms": round(prefill_ms, 3), "prefill_tokens_per_s": round(2048 / prefill_ms * 1e3),
+                                  "decode_batch": args.batch, "decode_ms_per_step": round(decode_ms, 3),
+                                  "decode_tokens_per_s": round(args.batch / decode_ms * 1e3), "launches_per_decode_step": launches,
+                                  "weight_bytes": engine.model.weight_bytes, "step_kinds": engine.step_kinds}), flush=True)
+                del engine
+                torch.cuda.empty_cache()
+        for line in mixer_kernels(torch, size, peak):
+            print(json.dumps(dict(line, size=name)), flush=True)
+    return 0
+
+
 def main():
     args = parse_args()
     if args.gpus != 1:
@@ -755,6 +929,8 @@ def main():
         return run_reference(args)
     if args.kernels:
         return run_kernels()
+    if args.compare:
+        return run_compare(args)
     return run_ours(args)
 
 

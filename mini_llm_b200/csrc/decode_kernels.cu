@@ -152,6 +152,8 @@ skinny_linear_kernel(const SkinnyParams p, int n_per_cta) {
             float v = mine + (p.bias ? p.bias[n] : 0.0f);
             if (p.epilogue == EPI_GELU_TANH) v = gelu_tanh_f(v);
             else if (p.epilogue == EPI_GELU_ERF) v = gelu_erf_f(v);
+            else if (p.epilogue == EPI_RELU_SQ) v = v > 0.0f ? v * v : 0.0f;
+            else if (p.epilogue == EPI_SILU) v = v / (1.0f + expf(-v));
             if (p.k_pages != nullptr && n >= p.q_width) {
                 int pos = p.positions[row];
                 int page = p.block_table[(long)p.token_item[row] * p.max_blocks + pos / p.page_size];

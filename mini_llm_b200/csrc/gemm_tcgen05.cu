@@ -68,6 +68,8 @@ struct GemmParams {
 __device__ __forceinline__ float activate(float v, int epilogue) {
     if (epilogue == EPI_GELU_TANH) return gelu_tanh_fast(v);
     if (epilogue == EPI_GELU_ERF) return gelu_erf_f(v);
+    if (epilogue == EPI_RELU_SQ) return v > 0.0f ? v * v : 0.0f;
+    if (epilogue == EPI_SILU) return v / (1.0f + __expf(-v));
     return v;
 }
 
@@ -92,6 +94,8 @@ __device__ __forceinline__ float load_from_rank(const float* mine, uint32_t rank
 template <int EPI> __device__ __forceinline__ float activate_as(float v) {
     if (EPI == EPI_GELU_TANH) return gelu_tanh_fast(v);
     if (EPI == EPI_GELU_ERF) return gelu_erf_f(v);
+    if (EPI == EPI_RELU_SQ) return v > 0.0f ? v * v : 0.0f;
+    if (EPI == EPI_SILU) return v / (1.0f + __expf(-v));
     return v;
 }
 
@@ -127,6 +131,8 @@ __device__ __forceinline__ void store_rows_bf16(const float* turn, bf16* base, R
                                                 bool col_ok, int lane, int rows_left, const float* bias, int epilogue) {
     if (epilogue == EPI_GELU_TANH) store_rows_bf16_as<EPI_GELU_TANH>(turn, base, row_offset, paired, col_ok, lane, rows_left, bias);
     else if (epilogue == EPI_GELU_ERF) store_rows_bf16_as<EPI_GELU_ERF>(turn, base, row_offset, paired, col_ok, lane, rows_left, bias);
+    else if (epilogue == EPI_RELU_SQ) store_rows_bf16_as<EPI_RELU_SQ>(turn, base, row_offset, paired, col_ok, lane, rows_left, bias);
+    else if (epilogue == EPI_SILU) store_rows_bf16_as<EPI_SILU>(turn, base, row_offset, paired, col_ok, lane, rows_left, bias);
     else store_rows_bf16_as<EPI_STORE>(turn, base, row_offset, paired, col_ok, lane, rows_left, bias);
 }
 
@@ -503,6 +509,8 @@ __device__ __forceinline__ void finish_block(BlockOut& o, const GemmParams& p, c
             if (wide) stage_row_f32(v, bias32, block, lane);
             else if (p.epilogue == EPI_GELU_TANH) stage_row_bf16<EPI_GELU_TANH>(v, bias32, block, lane);
             else if (p.epilogue == EPI_GELU_ERF) stage_row_bf16<EPI_GELU_ERF>(v, bias32, block, lane);
+            else if (p.epilogue == EPI_RELU_SQ) stage_row_bf16<EPI_RELU_SQ>(v, bias32, block, lane);
+            else if (p.epilogue == EPI_SILU) stage_row_bf16<EPI_SILU>(v, bias32, block, lane);
             else stage_row_bf16<EPI_STORE>(v, bias32, block, lane);
             fence_async_smem();
             __syncwarp();

@@ -423,6 +423,285 @@ extern "C" int mllm_sequence_latent_attention(float* out, const float* q_eff, co
 }
 
 // ---------------------------------------------------------------------------
+// The same attention in tiles: a block of 256 threads takes 32 query rows that share their
+// keys (TQ consecutive tokens of one request x HB heads, TQ * HB = 32) and walks the keys 32
+// at a time.  The rows' effective queries (32-bit) and the block of cached rows lie in shared
+// memory; scores, softmax and the weighted sum of the latents are 32-bit FMA in register
+// tiles (2 x 2 scores per thread; RPT rows x 8 * CT latent columns per thread), so a cached
+// row is read once for all heads of HB and all tokens of TQ instead of once per (token, head).
+//   prompt portions: `tiles` is the step's work list (records of 8 ints: entry, first row,
+//     rows <= 128, position of the first row, part, ...; records with part != 0 are skipped),
+//     every record is cut into pieces of TQ tokens (grid.x = records * 128 / TQ);
+//   single tokens: tiles is null, TQ = 1, grid.x = tokens, and grid.z = parts: part z takes the
+//     keys [z * keys_per_part, (z + 1) * keys_per_part) and leaves (max, sum, unnormalised result)
+//     for latent_merge_kernel.
+// ---------------------------------------------------------------------------
+struct LatentTiledParams {
+    float* out;                    // [T, heads * rank] (parts == 1)
+    float* part_out;               // [T, heads, parts, rank]
+    float* part_ml;                // [T, heads, parts, 2]
+    const float* q_eff;            // [T, heads * (rank + rot)]
+    const void* pages;
+    const int* block_table; const int* positions; const int* token_item; const int* tiles;
+    int max_blocks, page_size, n_tokens, heads, rank, rot, TQ, HB, parts, keys_per_part;
+    float scale;
+};
+
+template <typename T> struct Chunk4;
+template <> struct Chunk4<float> { typedef float4 type; };
+template <> struct Chunk4<bf16> { typedef uint2 type; };
+__device__ __forceinline__ void unpack4(const float4& c, float* v) { v[0] = c.x; v[1] = c.y; v[2] = c.z; v[3] = c.w; }
+__device__ __forceinline__ void unpack4(const uint2& c, float* v) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&c.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&c.y));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+
+template <typename T, int RPT, int CT>
+__global__ void __launch_bounds__(256)
+latent_attention_tiled_kernel(LatentTiledParams p) {
+    typedef typename Chunk4<T>::type chunk_t;
+    constexpr int R = 32, BK = 32, CG = 8 * RPT;
+    extern __shared__ __align__(16) unsigned char raw[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int row_width = p.rank + p.rot, ld = row_width + 4;
+    float* Qs = reinterpret_cast<float*>(raw);                      // [R][ld]
+    float* Ss = Qs + R * ld;                                        // [R][BK + 1]
+    float* factor = Ss + R * (BK + 1);                              // [R]: what the sums so far are multiplied by
+    float* sums = factor + R;                                       // [R]
+    T* Ks = reinterpret_cast<T*>(sums + R);                         // [BK][ld]
+    __shared__ int row_position[R];
+
+    int item, first_row, rows, first_position;
+    if (p.tiles != nullptr) {
+        const int pieces = 128 / p.TQ;
+        const int* record = p.tiles + (long)(blockIdx.x / pieces) * 8;
+        const int piece = blockIdx.x % pieces;
+        if (record[4] != 0 || piece * p.TQ >= record[2]) return;
+        item = record[0];
+        first_row = record[1] + piece * p.TQ;
+        rows = min(p.TQ, record[2] - piece * p.TQ);
+        first_position = record[3] + piece * p.TQ;
+    } else {
+        first_row = blockIdx.x;
+        item = p.token_item[first_row];
+        rows = 1;
+        first_position = p.positions[first_row];
+    }
+    const int head0 = blockIdx.y * p.HB;
+    const int* bt = p.block_table + (long)item * p.max_blocks;
+    int key_begin = 0, key_end = first_position + rows;            // keys [key_begin, key_end)
+    if (p.parts > 1) {
+        key_begin = blockIdx.z * p.keys_per_part;
+        key_end = min(key_end, key_begin + p.keys_per_part);
+    }
+    const bool empty = key_begin >= key_end;
+    // row r of the block: token r / HB of the piece, head head0 + r % HB
+    for (int i = tid; i < R * (row_width / 4); i += 256) {
+        const int r = i / (row_width / 4), c = (i % (row_width / 4)) * 4;
+        const int token = r / p.HB, head = head0 + r % p.HB;
+        float4 x = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (token < rows && head < p.heads)
+            x = *reinterpret_cast<const float4*>(p.q_eff + ((long)(first_row + token) * p.heads + head) * row_width + c);
+        *reinterpret_cast<float4*>(Qs + r * ld + c) = x;
+    }
+    if (tid < R) {
+        const int token = tid / p.HB;
+        row_position[tid] = first_position + (token < rows ? token : 0);
+    }
+    float m_row[4], l_row[4];                                       // of rows 4 * warp + i, the same in every lane
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        m_row[i] = -INFINITY;
+        l_row[i] = 0.0f;
+    }
+    float acc[RPT][8 * CT];
+#pragma unroll
+    for (int i = 0; i < RPT; i++)
+#pragma unroll
+        for (int c = 0; c < 8 * CT; c++) acc[i][c] = 0.0f;
+    const int rg = tid / CG, cg = tid % CG;
+    const int rp = tid >> 4, jp = tid & 15;
+
+    for (int k0 = key_begin; k0 < key_end; k0 += BK) {
+        __syncthreads();                                            // the block before is used up (and Qs is written)
+        for (int i = tid; i < BK * (row_width / 4); i += 256) {
+            const int j = i / (row_width / 4), c = (i % (row_width / 4)) * 4;
+            const int key = k0 + j;
+            chunk_t x;
+            memset(&x, 0, sizeof(x));
+            if (key < key_end) {
+                const T* row = reinterpret_cast<const T*>(p.pages) +
+                               ((long)bt[key / p.page_size] * p.page_size + (key % p.page_size)) * row_width;
+                x = *reinterpret_cast<const chunk_t*>(row + c);
+            }
+            *reinterpret_cast<chunk_t*>(Ks + j * ld + c) = x;
+        }
+        __syncthreads();
+        // scores: rows rp, rp + 16 against keys jp, jp + 16
+        {
+            float s00 = 0.0f, s01 = 0.0f, s10 = 0.0f, s11 = 0.0f;
+            for (int d = 0; d < row_width; d += 4) {
+                const float4 qa = *reinterpret_cast<const float4*>(Qs + rp * ld + d);
+                const float4 qb = *reinterpret_cast<const float4*>(Qs + (rp + 16) * ld + d);
+                float ka[4], kb[4];
+                unpack4(*reinterpret_cast<const chunk_t*>(Ks + jp * ld + d), ka);
+                unpack4(*reinterpret_cast<const chunk_t*>(Ks + (jp + 16) * ld + d), kb);
+                s00 = fmaf(qa.x, ka[0], fmaf(qa.y, ka[1], fmaf(qa.z, ka[2], fmaf(qa.w, ka[3], s00))));
+                s01 = fmaf(qa.x, kb[0], fmaf(qa.y, kb[1], fmaf(qa.z, kb[2], fmaf(qa.w, kb[3], s01))));
+                s10 = fmaf(qb.x, ka[0], fmaf(qb.y, ka[1], fmaf(qb.z, ka[2], fmaf(qb.w, ka[3], s10))));
+                s11 = fmaf(qb.x, kb[0], fmaf(qb.y, kb[1], fmaf(qb.z, kb[2], fmaf(qb.w, kb[3], s11))));
+            }
+            Ss[rp * (BK + 1) + jp] = s00;
+            Ss[rp * (BK + 1) + jp + 16] = s01;
+            Ss[(rp + 16) * (BK + 1) + jp] = s10;
+            Ss[(rp + 16) * (BK + 1) + jp + 16] = s11;
+        }
+        __syncthreads();
+        // softmax, online: warp w owns rows 4w .. 4w + 3, a lane a key
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int r = warp * 4 + i, key = k0 + lane;
+            const bool seen = key < key_end && key <= row_position[r];
+            const float sc = seen ? Ss[r * (BK + 1) + lane] * p.scale : -INFINITY;
+            const float m_new = fmaxf(m_row[i], warp_max(sc));
+            float c = 0.0f, e = 0.0f;
+            if (m_new != -INFINITY) {
+                c = expf(m_row[i] - m_new);
+                e = expf(sc - m_new);
+            }
+            l_row[i] = l_row[i] * c + warp_sum(e);
+            m_row[i] = m_new;
+            Ss[r * (BK + 1) + lane] = e;
+            if (lane == 0) factor[r] = c;
+        }
+        __syncthreads();
+        // weighted sum of the latents: rows rg * RPT + i, columns (ct * CG + cg) * 8 ..
+#pragma unroll
+        for (int i = 0; i < RPT; i++) {
+            const float c = factor[rg * RPT + i];
+#pragma unroll
+            for (int x = 0; x < 8 * CT; x++) acc[i][x] *= c;
+        }
+        for (int j = 0; j < BK; j++) {
+            float w[RPT];
+#pragma unroll
+            for (int i = 0; i < RPT; i++) w[i] = Ss[(rg * RPT + i) * (BK + 1) + j];
+#pragma unroll
+            for (int ct = 0; ct < CT; ct++) {
+                const int c0 = (ct * CG + cg) * 8;
+                if (c0 < p.rank) {
+                    float v[8];
+                    unpack4(*reinterpret_cast<const chunk_t*>(Ks + j * ld + c0), v);
+                    unpack4(*reinterpret_cast<const chunk_t*>(Ks + j * ld + c0 + 4), v + 4);
+#pragma unroll
+                    for (int i = 0; i < RPT; i++)
+#pragma unroll
+                        for (int x = 0; x < 8; x++) acc[i][ct * 8 + x] = fmaf(w[i], v[x], acc[i][ct * 8 + x]);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            sums[warp * 4 + i] = l_row[i];
+            factor[warp * 4 + i] = m_row[i];
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < RPT; i++) {
+        const int r = rg * RPT + i;
+        const int token = r / p.HB, head = head0 + r % p.HB;
+        if (token >= rows || head >= p.heads) continue;
+        const long at = (long)(first_row + token) * p.heads + head;
+#pragma unroll
+        for (int ct = 0; ct < CT; ct++) {
+            const int c0 = (ct * CG + cg) * 8;
+            if (c0 >= p.rank) continue;
+            if (p.parts > 1) {
+                float* o = p.part_out + (at * p.parts + blockIdx.z) * p.rank + c0;
+#pragma unroll
+                for (int x = 0; x < 8; x++) o[x] = empty ? 0.0f : acc[i][ct * 8 + x];
+            } else {
+                const float inv = 1.0f / sums[r];
+                float* o = p.out + at * p.rank + c0;
+#pragma unroll
+                for (int x = 0; x < 8; x++) o[x] = acc[i][ct * 8 + x] * inv;
+            }
+        }
+        if (p.parts > 1 && cg == 0) {
+            p.part_ml[(at * p.parts + blockIdx.z) * 2] = empty ? -INFINITY : factor[r];
+            p.part_ml[(at * p.parts + blockIdx.z) * 2 + 1] = empty ? 0.0f : sums[r];
+        }
+    }
+}
+
+// The parts of a (token, head) into one result, in the order of the parts.
+__global__ void latent_merge_kernel(float* __restrict__ out, const float* __restrict__ part_out,
+                                    const float* __restrict__ part_ml, int parts, int rank) {
+    const long at = blockIdx.x;
+    const float* ml = part_ml + at * parts * 2;
+    float big = -INFINITY;
+    for (int z = 0; z < parts; z++) big = fmaxf(big, ml[2 * z]);
+    float total = 0.0f;
+    for (int z = 0; z < parts; z++)
+        if (ml[2 * z] != -INFINITY) total += ml[2 * z + 1] * expf(ml[2 * z] - big);
+    for (int d = threadIdx.x; d < rank; d += blockDim.x) {
+        float o = 0.0f;
+        for (int z = 0; z < parts; z++)
+            if (ml[2 * z] != -INFINITY) o = fmaf(part_out[(at * parts + z) * rank + d], expf(ml[2 * z] - big), o);
+        out[at * rank + d] = o / total;
+    }
+}
+
+static size_t latent_tiled_shared_bytes(int row_width, int element_bytes) {
+    const size_t ld = (size_t)row_width + 4;
+    return 32 * ld * 4 + 32 * 33 * 4 + 64 * 4 + 32 * ld * (size_t)element_bytes;
+}
+
+template <typename T, int RPT, int CT>
+static int launch_latent_tiled(const LatentTiledParams& p, dim3 grid, size_t shared, cudaStream_t s) {
+    if (shared > 48 * 1024)
+        cudaFuncSetAttribute(latent_attention_tiled_kernel<T, RPT, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    latent_attention_tiled_kernel<T, RPT, CT><<<grid, 256, shared, s>>>(p);
+    return check_launch("latent_attention_tiled_kernel");
+}
+
+template <typename T>
+static int pick_latent_tiled(const LatentTiledParams& p, dim3 grid, size_t shared, cudaStream_t s) {
+    if (p.rank <= 128) return launch_latent_tiled<T, 2, 1>(p, grid, shared, s);
+    if (p.rank <= 256) return launch_latent_tiled<T, 4, 1>(p, grid, shared, s);
+    if (p.rank <= 512) return launch_latent_tiled<T, 8, 1>(p, grid, shared, s);
+    return launch_latent_tiled<T, 8, 2>(p, grid, shared, s);
+}
+
+// n_units: records of `tiles` (prompt portions), or tokens (tiles null: single tokens, in `parts` parts).
+extern "C" int mllm_sequence_latent_attention_tiled(const LatentTiledParams* params, int n_units, int dtype, void* stream) {
+    LatentTiledParams p = *params;
+    if (n_units <= 0) return 0;
+    const int row_width = p.rank + p.rot;
+    if (row_width % 4 != 0 || p.rank % 8 != 0 || p.rank > 1024) return fail("latent_attention_tiled: the row must be a multiple of 4 and the latent of 8, at most 1024");
+    if (p.HB <= 0 || p.TQ <= 0 || p.HB * p.TQ != 32 || 128 % p.TQ != 0) return fail("latent_attention_tiled: a block takes 32 rows");
+    if (p.tiles == nullptr && p.TQ != 1) return fail("latent_attention_tiled: single tokens come one per block");
+    if (p.parts < 1 || (p.parts > 1 && (p.tiles != nullptr || p.keys_per_part <= 0 || p.part_out == nullptr || p.part_ml == nullptr)))
+        return fail("latent_attention_tiled: parts are for single tokens and need scratch");
+    const size_t shared = latent_tiled_shared_bytes(row_width, dtype == DT_F32 ? 4 : 2);
+    if (shared > 220 * 1024) return fail("latent_attention_tiled: the rows do not fit in shared memory");
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(p.tiles != nullptr ? n_units * (128 / p.TQ) : n_units, (p.heads + p.HB - 1) / p.HB, p.parts);
+    int rc;
+    if (dtype == DT_F32) rc = pick_latent_tiled<float>(p, grid, shared, s);
+    else if (dtype == DT_BF16) rc = pick_latent_tiled<bf16>(p, grid, shared, s);
+    else return fail("latent_attention_tiled: unknown dtype");
+    if (rc != 0 || p.parts == 1) return rc;
+    latent_merge_kernel<<<(unsigned)((long)n_units * p.heads), 128, 0, s>>>(p.out, p.part_out, p.part_ml, p.parts, p.rank);
+    return check_launch("latent_merge_kernel");
+}
+
+// ---------------------------------------------------------------------------
 // Matrix memory, token by token.  Per (request, head): S [dim, vdim] with
 //   S <- a S + b k v^T,   o = S^T q
 // either with a fixed decay per head (a = decay[head], b = 1), or gated and stabilised:
@@ -562,6 +841,264 @@ extern "C" int mllm_sequence_memory_scan(const MemoryScanParams* params, int n_i
         return fail("memory_scan: unknown dtype");
     }
     return check_launch("memory_scan_kernel");
+}
+
+// ---------------------------------------------------------------------------
+// The same recurrence for prompt portions, a chunk of 32 tokens at a time.  Within a chunk
+// nothing is sequential but two prefix scans over the gates: with F_t the sum of the log
+// forget gates up to t and b_s = li_s - F_s,
+//   M_t = max(m_before, b_0 .. b_t),   m_t = F_t + M_t         (the running maximum)
+//   S_t = exp(m_before - M_t) S_before + sum_{s <= t} exp(b_s - M_t) k_s v_s^T
+// (every exponent is <= 0), and likewise n_t; with a fixed decay the weights are its powers,
+// taken from a table built by repeated multiplication.  So a chunk is three small products in
+// 32-bit FMA, spread over 256 threads:  A[t, s] = (q_t . k_s) weight[t, s];
+// o_t = carried weight_t (q_t S_before) + sum_s A[t, s] v_s;   S <- weight_last S + sum_s weight[last, s] k_s v_s^T.
+// n_t . q_t = carried weight_t (n_before . q_t) + sum_s A[t, s].  One block per (entry, head,
+// slice of 32 value columns).  Results differ from the token-by-token kernel by rounding only
+// (other order of the sums); decays, gates and state stay 32-bit.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+memory_chunk_kernel(MemoryScanParams p) {
+    constexpr int C = 32, VS = 32;
+    extern __shared__ __align__(16) float shared[];
+    const int item = blockIdx.x, head = blockIdx.y, v0 = blockIdx.z * VS, tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int count = p.item_count[item];
+    if (count <= 0) return;
+    const int dim = p.dim, vdim = p.vdim, heads = p.heads;
+    const int dimp = (dim + 3) & ~3, ldq = dimp + 4;
+    const bool gated = p.gates != nullptr;
+    float* qs = shared;                   // [C][ldq]
+    float* ks = qs + C * ldq;             // [C][ldq]
+    float* vs = ks + C * ldq;             // [C][VS]
+    float* S = vs + C * VS;               // [dimp][VS]
+    float* A = S + dimp * VS;             // [C][C + 4]
+    float* nv = A + C * (C + 4);          // [dimp]
+    float* bs = nv + dimp;                // [C]      b_s
+    float* Mt = bs + C;                   // [C]      M_t
+    float* Fs = Mt + C;                   // [C]      F_t
+    float* wt = Fs + C;                   // [C]      weight of the carried state at t
+    float* nq = wt + C;                   // [C]      n_before . q_t
+    float* dl = nq + C;                   // [C]      weight[last, s]
+    float* pw = dl + C;                   // [C + 1]  powers of a fixed decay
+    float* held = p.state + (long)p.item_slot[item] * p.state_stride;
+    float* S_held = held + (long)head * dim * vdim;
+    float* n_held = held + (long)heads * dim * vdim + (long)head * dim;
+    float* m_held = held + (long)heads * dim * vdim + (long)heads * dim + head;
+    for (int i = tid; i < dimp * VS; i += 256) {
+        const int d = i / VS, c = v0 + (i % VS);
+        S[i] = (d < dim && c < vdim) ? S_held[(long)d * vdim + c] : 0.0f;
+    }
+    for (int d = tid; d < dimp; d += 256) nv[d] = (gated && d < dim) ? n_held[d] : 0.0f;
+    float m_before = gated ? *m_held : 0.0f;
+    if (!gated && tid == 0) {
+        float power = 1.0f;
+        for (int i = 0; i <= C; i++) {
+            pw[i] = power;
+            power *= p.decay[head];
+        }
+    }
+    const long first = p.item_offset[item];
+    const T* q = (const T*)p.q + (long)head * dim;
+    const T* k = (const T*)p.k + (long)head * dim;
+    const T* v = (const T*)p.v + (long)head * vdim;
+    const int t_mine = tid >> 3, vg = tid & 7;
+    for (int done = 0; done < count; done += C) {
+        const int n = min(C, count - done), last = n - 1;
+        const long row0 = first + done;
+        __syncthreads();                  // the chunk before is done with everything
+        for (int i = tid; i < C * dimp; i += 256) {
+            const int t = i / dimp, d = i % dimp;
+            float qd = 0.0f, kd = 0.0f;
+            if (t < n && d < dim) {
+                qd = to_f32(q[(row0 + t) * p.ld_q + d]);
+                kd = to_f32(k[(row0 + t) * p.ld_k + d]);
+                if (p.silu) {
+                    qd = silu_f(qd);
+                    kd = silu_f(kd);
+                }
+                qd *= p.q_scale;
+            }
+            qs[t * ldq + d] = qd;
+            ks[t * ldq + d] = kd;
+        }
+        for (int i = tid; i < C * VS; i += 256) {
+            const int t = i / VS, c = v0 + (i % VS);
+            float x = (t < n && c < vdim) ? to_f32(v[(row0 + t) * p.ld_v + c]) : 0.0f;
+            if (p.silu) x = silu_f(x);
+            vs[i] = x;
+        }
+        if (gated && warp == 0) {
+            float lf = 0.0f, li = -INFINITY;
+            if (lane < n) {
+                const float gi = p.gates[(row0 + lane) * p.ld_gates + head] + p.gate_bias[head];
+                const float gf = p.gates[(row0 + lane) * p.ld_gates + heads + head] + p.gate_bias[heads + head];
+                li = p.gate_cap * tanhf(gi / p.gate_cap);
+                lf = log_sigmoid_f(p.gate_cap * tanhf(gf / p.gate_cap));
+            }
+            float F = lf;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float up = __shfl_up_sync(0xffffffffu, F, o);
+                if (lane >= o) F += up;
+            }
+            const float b = li - F;
+            float M = b;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float up = __shfl_up_sync(0xffffffffu, M, o);
+                if (lane >= o) M = fmaxf(M, up);
+            }
+            M = fmaxf(M, m_before);
+            const float M_last = __shfl_sync(0xffffffffu, M, last);
+            bs[lane] = b;
+            Mt[lane] = M;
+            Fs[lane] = F;
+            wt[lane] = expf(m_before - M);
+            dl[lane] = lane <= last ? expf(b - M_last) : 0.0f;
+        }
+        if (!gated && warp == 0) {
+            wt[lane] = pw[lane + 1];
+            dl[lane] = lane <= last ? pw[last - lane] : 0.0f;
+        }
+        __syncthreads();
+        // A[t, s] = (q_t . k_s) weight[t, s];  nq[t] = n_before . q_t
+        {
+            const int sg = tid & 7;
+            float dot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            for (int d = 0; d < dimp; d += 4) {
+                const float4 q4 = *reinterpret_cast<const float4*>(qs + t_mine * ldq + d);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(ks + (sg + 8 * i) * ldq + d);
+                    dot[i] = fmaf(q4.x, k4.x, fmaf(q4.y, k4.y, fmaf(q4.z, k4.z, fmaf(q4.w, k4.w, dot[i]))));
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int s_at = sg + 8 * i;
+                float weight = 0.0f;
+                if (s_at <= t_mine && s_at < n) weight = gated ? expf(bs[s_at] - Mt[t_mine]) : pw[t_mine - s_at];
+                A[t_mine * (C + 4) + s_at] = dot[i] * weight;
+            }
+            if (gated) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int t = warp * 4 + i;
+                    float part = 0.0f;
+                    for (int d = lane; d < dimp; d += 32) part = fmaf(nv[d], qs[t * ldq + d], part);
+                    part = warp_sum(part);
+                    if (lane == 0) nq[t] = part;
+                }
+            }
+        }
+        __syncthreads();
+        // o_t = carried weight_t (q_t S_before) + sum_s A[t, s] v_s
+        {
+            float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (int d = 0; d < dimp; d += 4) {
+                const float4 q4 = *reinterpret_cast<const float4*>(qs + t_mine * ldq + d);
+                const float qd[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float4 s4 = *reinterpret_cast<const float4*>(S + (d + i) * VS + vg * 4);
+                    acc.x = fmaf(qd[i], s4.x, acc.x);
+                    acc.y = fmaf(qd[i], s4.y, acc.y);
+                    acc.z = fmaf(qd[i], s4.z, acc.z);
+                    acc.w = fmaf(qd[i], s4.w, acc.w);
+                }
+            }
+            const float carried = wt[t_mine];
+            acc.x *= carried; acc.y *= carried; acc.z *= carried; acc.w *= carried;
+            float row_sum = 0.0f;
+            for (int s_at = 0; s_at <= t_mine; s_at++) {
+                const float a = A[t_mine * (C + 4) + s_at];
+                const float4 v4 = *reinterpret_cast<const float4*>(vs + s_at * VS + vg * 4);
+                acc.x = fmaf(a, v4.x, acc.x);
+                acc.y = fmaf(a, v4.y, acc.y);
+                acc.z = fmaf(a, v4.z, acc.z);
+                acc.w = fmaf(a, v4.w, acc.w);
+                row_sum += a;
+            }
+            if (gated) {
+                const float below = fmaxf(fabsf(fmaf(carried, nq[t_mine], row_sum)), expf(-(Fs[t_mine] + Mt[t_mine]))) + 1e-6f;
+                acc.x /= below; acc.y /= below; acc.z /= below; acc.w /= below;
+            }
+            if (t_mine < n) {
+                float* o = p.out + (row0 + t_mine) * p.ld_out + (long)head * vdim + v0 + vg * 4;
+                const int left = vdim - (v0 + vg * 4);
+                if (left > 0) o[0] = acc.x;
+                if (left > 1) o[1] = acc.y;
+                if (left > 2) o[2] = acc.z;
+                if (left > 3) o[3] = acc.w;
+            }
+        }
+        __syncthreads();
+        // S <- weight_last S + sum_s weight[last, s] k_s v_s^T;  n likewise;  m <- m_last
+        {
+            const float carried = wt[last];
+            for (int d = t_mine; d < dimp; d += 32) {
+                float4 s4 = *reinterpret_cast<const float4*>(S + d * VS + vg * 4);
+                s4.x *= carried; s4.y *= carried; s4.z *= carried; s4.w *= carried;
+                for (int s_at = 0; s_at < n; s_at++) {
+                    const float kd = ks[s_at * ldq + d] * dl[s_at];
+                    const float4 v4 = *reinterpret_cast<const float4*>(vs + s_at * VS + vg * 4);
+                    s4.x = fmaf(kd, v4.x, s4.x);
+                    s4.y = fmaf(kd, v4.y, s4.y);
+                    s4.z = fmaf(kd, v4.z, s4.z);
+                    s4.w = fmaf(kd, v4.w, s4.w);
+                }
+                *reinterpret_cast<float4*>(S + d * VS + vg * 4) = s4;
+            }
+            if (gated) {
+                for (int d = tid; d < dimp; d += 256) {
+                    float x = carried * nv[d];
+                    for (int s_at = 0; s_at < n; s_at++) x = fmaf(dl[s_at], ks[s_at * ldq + d], x);
+                    nv[d] = x;
+                }
+                m_before = Fs[last] + Mt[last];
+            }
+        }
+    }
+    __syncthreads();
+    if (!p.writes) return;
+    for (int i = tid; i < dimp * VS; i += 256) {
+        const int d = i / VS, c = v0 + (i % VS);
+        if (d < dim && c < vdim) S_held[(long)d * vdim + c] = S[i];
+    }
+    if (gated && blockIdx.z == 0) {
+        for (int d = tid; d < dim; d += 256) n_held[d] = nv[d];
+        if (tid == 0) *m_held = m_before;
+    }
+}
+
+static size_t memory_chunk_shared_bytes(int dim) {
+    const int dimp = (dim + 3) & ~3, ldq = dimp + 4;
+    return ((size_t)2 * 32 * ldq + 32 * 32 + (size_t)dimp * 32 + 32 * 36 + dimp + 6 * 32 + 33) * sizeof(float);
+}
+
+// Whether the chunked kernel takes the key size (its chunk of q and k, and a slice of the state, in shared memory).
+extern "C" int mllm_sequence_memory_chunk_takes(int dim) { return memory_chunk_shared_bytes(dim) <= 200 * 1024; }
+
+extern "C" int mllm_sequence_memory_chunk(const MemoryScanParams* params, int n_items, int dtype, void* stream) {
+    MemoryScanParams p = *params;
+    if (n_items <= 0) return 0;
+    if (p.heads <= 0 || p.heads > 65535 || p.dim <= 0 || p.vdim <= 0) return fail("memory_chunk: bad sizes");
+    const size_t shared = memory_chunk_shared_bytes(p.dim);
+    if (shared > 200 * 1024) return fail("memory_chunk: the key size is too large for a chunk in shared memory");
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(n_items, p.heads, (p.vdim + 31) / 32);
+    if (dtype == DT_F32) {
+        if (shared > 48 * 1024) cudaFuncSetAttribute(memory_chunk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        memory_chunk_kernel<float><<<grid, 256, shared, s>>>(p);
+    } else if (dtype == DT_BF16) {
+        if (shared > 48 * 1024) cudaFuncSetAttribute(memory_chunk_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        memory_chunk_kernel<bf16><<<grid, 256, shared, s>>>(p);
+    } else {
+        return fail("memory_chunk: unknown dtype");
+    }
+    return check_launch("memory_chunk_kernel");
 }
 
 // ---------------------------------------------------------------------------

@@ -112,14 +112,37 @@ class Kernels:
 
     def latent_attention(self, ctx, out, q_eff, cache, heads, rank, rot, scale):
         self.launches += 1
-        self.chose("latent_attention", "latent_attention_plain", q_eff.shape[0], heads, rank + rot)
+        n = q_eff.shape[0]
+        if not self.plain_only and ops.latent_attention_tiled_takes(cache.k_pages, rank, rot):
+            common = (out, q_eff, cache.k_pages, cache.block_table, ctx.positions, ctx.token_item, heads, rank, rot,
+                      cache.page_size, scale)
+            if ctx.att_tiles is not None:
+                # prompt portions: 32 rows (tokens x heads) a block share every cached row they read
+                self.chose("latent_attention", "latent_attention_tiled", n, heads, rank + rot)
+                return ops.latent_attention_tiled(*common, tiles=ctx.att_tiles, n_tiles=ctx.n_att_tiles)
+            if ctx.decode_only:
+                # single tokens: all heads of a token share the cached rows; while the (token, head
+                # block) pairs are fewer than twice the SMs, each token's keys come in parts
+                reach = cache.block_table.shape[1] * cache.page_size
+                blocks = n * -(-heads // ops.LATENT_TILE_ROWS)
+                parts = max(1, min(32, 296 // blocks, -(-reach // 64)))
+                per_part = -(-(-(-reach // parts)) // 32) * 32
+                scratch = self._latent_scratch(ctx.device, n * heads * parts * rank, n * heads * parts * 2) if parts > 1 else None
+                self.launches += 1 if parts > 1 else 0
+                self.chose("latent_attention", "latent_attention_tiled_parts", n, heads, rank + rot)
+                return ops.latent_attention_tiled(*common, parts=parts, keys_per_part=per_part, scratch=scratch)
+        self.chose("latent_attention", "latent_attention_plain", n, heads, rank + rot)
         return ops.latent_attention_plain(out, q_eff, cache.k_pages, cache.block_table, ctx.positions, ctx.token_item,
                                           heads, rank, rot, cache.page_size, scale)
 
     def memory_scan(self, ctx, out, q, k, v, state, heads, dim, vdim, writes=True, **how):
         self.launches += 1
+        # prompt portions go through the kernel that takes 32 tokens at a time; a step of single
+        # tokens walks each token's one update (the state is read and written once either way)
+        chunked = not ctx.decode_only and ops.memory_chunk_takes(dim)
+        self.chose("memory_scan", "memory_chunk" if chunked else "memory_scan", q.shape[0], heads, dim, vdim)
         return ops.memory_scan(out, q, k, v, state, ctx.item_slot, ctx.item_offset, ctx.item_count, heads, dim, vdim,
-                               writes=writes, **how)
+                               writes=writes, chunked=chunked, **how)
 
     def depth_mix(self, hidden, kept, weights, index):
         self.launches += 1
@@ -290,6 +313,15 @@ class Kernels:
         self.chose("attention", "attention_plain", n, n_heads, head_size)
         return ops.attention_plain(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions,
                                    ctx.token_item, n_heads, n_kv_heads, head_size, cache.page_size, scale, window)
+
+    def _latent_scratch(self, device, floats, pairs):
+        """Partial results of single tokens' latent attention in parts; grows when a step needs more."""
+        held = getattr(self, "_latent_parts", None)
+        if held is None or held[0].numel() < floats or held[1].numel() < pairs:
+            self._latent_parts = held = (torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device),
+                                         torch.empty(max(pairs, 1 << 14), dtype=torch.float32, device=device))
+            self.scratch_generation += 1
+        return held
 
     def attention_work(self, device):
         """The work counter of the persistent prompt-attention kernel (zero between launches)."""

@@ -16,7 +16,7 @@ from .lib import F, I, L, P, Function, KernelError, set_dependent_launch  # noqa
 
 DT_F32, DT_BF16 = 0, 1
 EPILOGUES = {"store": 0, "gelu_tanh": 1, "gelu_erf": 2, "add": 3, "relu_squared": 4, "silu": 5}
-GEMM_EPILOGUES = ("store", "gelu_tanh", "gelu_erf", "add")      # what the tensor-core and few-row kernels apply
+GEMM_EPILOGUES = tuple(EPILOGUES)      # what the tensor-core and few-row kernels apply
 
 _DTYPE_CODE = {torch.float32: DT_F32, torch.bfloat16: DT_BF16}
 
@@ -914,6 +914,79 @@ def latent_attention_plain(out, q_eff, pages, block_table, positions, token_item
     return out
 
 
+class _LatentTiledParams(ctypes.Structure):
+    _fields_ = [("out", P), ("part_out", P), ("part_ml", P), ("q_eff", P), ("pages", P), ("block_table", P),
+                ("positions", P), ("token_item", P), ("tiles", P), ("max_blocks", I), ("page_size", I), ("n_tokens", I),
+                ("heads", I), ("rank", I), ("rot", I), ("TQ", I), ("HB", I), ("parts", I), ("keys_per_part", I),
+                ("scale", F)]
+
+
+_latent_attention_tiled = Function("sequence", "mllm_sequence_latent_attention_tiled",
+                                   [ctypes.POINTER(_LatentTiledParams), I, I, P])
+LATENT_TILE_ROWS = 32
+
+
+def latent_attention_tiled_takes(pages, rank, rot) -> bool:
+    """Whether the tiled kernel takes the sizes: rows of a multiple of 4 entries whose latent part is
+    a multiple of 8 (at most 1024), and 32 effective queries plus 32 cached rows in shared memory."""
+    row = rank + rot
+    shared = 32 * (row + 4) * 4 + 32 * 33 * 4 + 64 * 4 + 32 * (row + 4) * pages.element_size()
+    return row % 4 == 0 and rank % 8 == 0 and rank <= 1024 and shared <= 220 * 1024
+
+
+def latent_heads_per_block(heads: int) -> int:
+    """Heads of one block of 32 rows in prompt portions: the power of two at or above the number of
+    heads, 32 at most; the block then takes 32 / that many consecutive tokens."""
+    block = 1
+    while block < min(heads, LATENT_TILE_ROWS):
+        block *= 2
+    return block
+
+
+def latent_attention_tiled(out, q_eff, pages, block_table, positions, token_item, heads, rank, rot, page_size, scale,
+                           tiles=None, n_tiles=0, parts=1, keys_per_part=0, scratch=None):
+    """``latent_attention_plain`` in tiles of 32 query rows that share their keys.  With ``tiles``
+    (the step's work list, device int32 records of 8, ``n_tiles`` of them) for prompt portions;
+    without, for single tokens, the keys of each in ``parts`` parts of ``keys_per_part`` keys whose
+    results are merged (``scratch``: fp32 (T * heads * parts * rank, T * heads * parts * 2))."""
+    _check(out, "latent_attention.out", torch.float32, 2)
+    _check(q_eff, "latent_attention.q_eff", torch.float32, 2)
+    _check(pages, "latent_attention.pages")
+    _check(block_table, "latent_attention.block_table", torch.int32, 2)
+    n = q_eff.shape[0]
+    if (not out.is_contiguous() or not q_eff.is_contiguous() or out.shape != (n, heads * rank)
+            or q_eff.shape[1] != heads * (rank + rot) or not pages.is_contiguous() or not block_table.is_contiguous()):
+        raise KernelError("latent_attention: sizes do not agree")
+    if not latent_attention_tiled_takes(pages, rank, rot):
+        raise KernelError(f"latent_attention_tiled does not take rows of {rank} + {rot}")
+    params = _LatentTiledParams()
+    params.out, params.q_eff, params.pages = out.data_ptr(), q_eff.data_ptr(), pages.data_ptr()
+    params.block_table, params.positions, params.token_item = block_table.data_ptr(), positions.data_ptr(), token_item.data_ptr()
+    params.max_blocks, params.page_size, params.n_tokens = block_table.shape[1], page_size, n
+    params.heads, params.rank, params.rot, params.scale = heads, rank, rot, float(scale)
+    if tiles is not None:
+        _check(tiles, "latent_attention.tiles", torch.int32)
+        if tiles.numel() < ATTENTION_TILE_RECORD * n_tiles or parts != 1:
+            raise KernelError("latent_attention_tiled: the work list is shorter than stated, or parts were asked for")
+        params.tiles = tiles.data_ptr()
+        params.HB = latent_heads_per_block(heads)
+        params.TQ = LATENT_TILE_ROWS // params.HB
+        params.parts, units = 1, n_tiles
+    else:
+        params.HB, params.TQ, params.parts, params.keys_per_part, units = LATENT_TILE_ROWS, 1, int(parts), int(keys_per_part), n
+        if parts > 1:
+            part_out, part_ml = scratch
+            _check(part_out, "latent_attention.scratch", torch.float32)
+            _check(part_ml, "latent_attention.scratch", torch.float32)
+            if part_out.numel() < n * heads * parts * rank or part_ml.numel() < n * heads * parts * 2:
+                raise KernelError("latent_attention_tiled: scratch too small")
+            if keys_per_part * parts < page_size * block_table.shape[1]:
+                raise KernelError("latent_attention_tiled: the parts do not cover the longest block table")
+            params.part_out, params.part_ml = part_out.data_ptr(), part_ml.data_ptr()
+    _latent_attention_tiled(ctypes.byref(params), units, dtype_code(pages.dtype), _stream())
+    return out
+
+
 class _MemoryScanParams(ctypes.Structure):
     _fields_ = [("out", P), ("ld_out", L), ("q", P), ("k", P), ("v", P), ("ld_q", L), ("ld_k", L), ("ld_v", L),
                 ("gates", P), ("ld_gates", L), ("gate_bias", P), ("decay", P), ("state", P), ("state_stride", L),
@@ -922,6 +995,14 @@ class _MemoryScanParams(ctypes.Structure):
 
 
 _memory_scan = Function("sequence", "mllm_sequence_memory_scan", [ctypes.POINTER(_MemoryScanParams), I, I, P])
+_memory_chunk = Function("sequence", "mllm_sequence_memory_chunk", [ctypes.POINTER(_MemoryScanParams), I, I, P])
+
+
+def memory_chunk_takes(dim) -> bool:
+    """Whether the chunked kernel takes the key size: a chunk's q and k and a slice of the state
+    lie in shared memory (the launcher's own arithmetic)."""
+    padded = (dim + 3) & ~3
+    return 4 * (2 * 32 * (padded + 4) + 32 * 32 + padded * 32 + 32 * 36 + padded + 6 * 32 + 33) <= 200 * 1024
 
 
 def memory_state_floats(heads, dim, vdim, gated) -> int:
@@ -931,13 +1012,15 @@ def memory_state_floats(heads, dim, vdim, gated) -> int:
 
 
 def memory_scan(out, q, k, v, state, item_slot, item_offset, item_count, heads, dim, vdim, q_scale=1.0, silu=False,
-                gates=None, gate_bias=None, gate_cap=0.0, decay=None, writes=True):
+                gates=None, gate_bias=None, gate_cap=0.0, decay=None, writes=True, chunked=False):
     """The matrix-memory recurrence over each entry's tokens, in order:
     S <- a S + b k v^T, out = S^T q, with a fixed decay per head (``decay`` [heads]; a = decay,
     b = 1) or with ``gates`` [T, 2 * heads] (fp32: input gates then forget gates, ``gate_bias``
     added): capped, exponential, stabilised by a running maximum, the output divided by
     max(|n . q|, exp(-m)) + 1e-6.  q, k [T, heads * dim], v [T, heads * vdim] (any row stride);
-    out fp32 [T, heads * vdim]; ``state`` fp32 [slots, memory_state_floats(...)]."""
+    out fp32 [T, heads * vdim]; ``state`` fp32 [slots, memory_state_floats(...)].
+    ``chunked``: the kernel for prompt portions, which takes 32 tokens at a time (the same sums in
+    another order); without, every token is a step of its own (single decoded tokens)."""
     _check(out, "memory_scan.out", torch.float32, 2)
     for name, t in (("q", q), ("k", k), ("v", v)):
         _check(t, f"memory_scan.{name}", q.dtype, 2)
@@ -968,7 +1051,9 @@ def memory_scan(out, q, k, v, state, item_slot, item_offset, item_count, heads, 
     params.heads, params.dim, params.vdim = heads, dim, vdim
     params.q_scale, params.gate_cap = float(q_scale), float(gate_cap)
     params.silu, params.writes = int(bool(silu)), int(bool(writes))
-    _memory_scan(ctypes.byref(params), item_count.shape[0], dtype_code(q.dtype), _stream())
+    if chunked and not memory_chunk_takes(dim):
+        raise KernelError(f"memory_scan: the chunked kernel does not take a key size of {dim}")
+    (_memory_chunk if chunked else _memory_scan)(ctypes.byref(params), item_count.shape[0], dtype_code(q.dtype), _stream())
     return out
 
 

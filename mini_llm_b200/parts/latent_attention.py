@@ -27,6 +27,7 @@ from .spec import PagedKV, WeightSpec
 
 class LatentAttention(Mixer):
     graph_safe = True
+    wants_attention_tiles = True      # its prompt kernel reads the step's work list of (up to 128 tokens, entry) tiles
 
     def __init__(self, prefix, width: int, n_heads: int, head_size: int, rotated_size: int, value_size: int,
                  latent_size: int, score_scale: float, rotary_base: float, rotary_dims: int, eps: float,

@@ -109,7 +109,7 @@ def test_a_mixer_with_state_of_its_own_registers_builds_and_steps(tmp_path):
     assert json.load(open(os.path.join(folder, "config.json")))["architectures"] == ["ToyDecayLM"]
     engine = Engine(folder, dtype="float32", max_requests=3)
     assert [g.paged for g in engine.cache.groups] == [False]
-    assert engine.storage.states[0].shape == (3, 3, 48)        # three run entries, three slots
+    assert engine.storage.states[0].shape == (3, 4, 48)        # three run entries; three slots and the filler tokens' own
     requests = {"u": random_tokens(1, 23, 201), "v": random_tokens(2, 9, 201), "w": random_tokens(3, 40, 201)}
     for steps in (schedule_whole(requests), schedule_portions(requests, sizes=(5, 2, 3, 7)),
                   [[("u", 10), ("v", 4)], [("u", 1), ("v", 1), ("w", 13)], [("u", 12), ("v", 4), ("w", 27)]]):
