@@ -819,13 +819,10 @@ def mixer_kernels(torch, size: dict, peak: dict):
                                                                          rank, rot, page, 0.1, tiles=tiles_d, n_tiles=len(tiles)))
             add(f"latent attention in tiles, {name}", us, flops=2.0 * pairs * (row + rank), heads=heads, row=row)
         else:
-            reach = table.shape[1] * page
-            parts = max(1, min(32, 296 // (n * -(-heads // 32)), reach // 64))
-            per_part = -(-(-(-reach // parts)) // 32) * 32
+            parts = max(1, min(32, 296 // (n * -(-heads // 32))))
             scratch = (torch.empty(n * heads * parts * rank, device="cuda"), torch.empty(n * heads * parts * 2, device="cuda"))
             us = replayed_us(torch, lambda i: ops.latent_attention_tiled(out, q_eff, pages[i % 4], table, positions, token_item, heads,
-                                                                         rank, rot, page, 0.1, parts=parts, keys_per_part=per_part,
-                                                                         scratch=scratch))
+                                                                         rank, rot, page, 0.1, parts=parts, scratch=scratch))
             add(f"latent attention in parts, {name}", us, bytes_moved=sum(lengths) * row * 2.0, heads=heads, row=row, parts=parts)
         # GPT-2's kernels at as many heads of 64
         head = 64

@@ -297,6 +297,38 @@ head_linear_kernel(OT* __restrict__ out, const AT* __restrict__ a, const WT* __r
     }
 }
 
+// The same for up to 16 rows (a step of single tokens): a block takes eight output features of one
+// head, a warp one of them; the head's rows of `a` lie in shared memory (32-bit), the weight row is
+// read once, 16 bytes a lane where K allows it.
+template <typename AT, typename WT, typename OT>
+__global__ void __launch_bounds__(256)
+head_linear_few_rows_kernel(OT* __restrict__ out, const AT* __restrict__ a, const WT* __restrict__ w, int M, int N, int K,
+                            long lda, long ldo, long a_head, long o_head) {
+    extern __shared__ float rows[];                 // [M][K]
+    const int head = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    a += (long)head * a_head;
+    for (int i = threadIdx.x; i < M * K; i += 256) rows[i] = to_f32(a[(long)(i / K) * lda + (i % K)]);
+    __syncthreads();
+    const int n = blockIdx.x * 8 + warp;
+    if (n >= N) return;
+    const WT* weights = w + ((long)head * N + n) * K;
+    float acc[16];
+#pragma unroll
+    for (int m = 0; m < 16; m++) acc[m] = 0.0f;
+    for (int k = lane; k < K; k += 32) {
+        const float x = to_f32(weights[k]);
+#pragma unroll
+        for (int m = 0; m < 16; m++)
+            if (m < M) acc[m] = fmaf(rows[m * K + k], x, acc[m]);
+    }
+#pragma unroll
+    for (int m = 0; m < 16; m++) {
+        if (m >= M) break;
+        const float total = warp_sum(acc[m]);
+        if (lane == 0) out[(long)m * ldo + (long)head * o_head + n] = from_f32<OT>(total);
+    }
+}
+
 extern "C" int mllm_sequence_head_linear(void* out, const void* a, const void* w, int M, int N, int K, int heads, long lda,
                                          long ldo, long a_head, long o_head, int a_dtype, int w_dtype, int out_dtype,
                                          void* stream) {
@@ -305,13 +337,19 @@ extern "C" int mllm_sequence_head_linear(void* out, const void* a, const void* w
     if ((M + 63) / 64 > 65535 || heads > 65535) return fail("head_linear: too many rows or heads for one launch");
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid((N + 63) / 64, (M + 63) / 64, heads);
-#define MLLM_HEAD_LINEAR(AT, WT, OT)                                                                             \
-    head_linear_kernel<AT, WT, OT><<<grid, 256, 0, s>>>((OT*)out, (const AT*)a, (const WT*)w, M, N, K, lda, ldo, \
-                                                        a_head, o_head)
-    if (a_dtype == DT_F32 && w_dtype == DT_F32 && out_dtype == DT_F32) MLLM_HEAD_LINEAR(float, float, float);
-    else if (a_dtype == DT_BF16 && w_dtype == DT_BF16 && out_dtype == DT_F32) MLLM_HEAD_LINEAR(bf16, bf16, float);
-    else if (a_dtype == DT_F32 && w_dtype == DT_BF16 && out_dtype == DT_BF16) MLLM_HEAD_LINEAR(float, bf16, bf16);
-    else if (a_dtype == DT_BF16 && w_dtype == DT_BF16 && out_dtype == DT_BF16) MLLM_HEAD_LINEAR(bf16, bf16, bf16);
+    const bool few = M <= 16 && (size_t)M * K * sizeof(float) <= 48 * 1024;
+    dim3 few_grid((N + 7) / 8, heads);
+#define MLLM_HEAD_LINEAR(AT, WT, OT)                                                                                  \
+    if (few)                                                                                                          \
+        head_linear_few_rows_kernel<AT, WT, OT><<<few_grid, 256, (size_t)M * K * sizeof(float), s>>>(                 \
+            (OT*)out, (const AT*)a, (const WT*)w, M, N, K, lda, ldo, a_head, o_head);                                 \
+    else                                                                                                              \
+        head_linear_kernel<AT, WT, OT><<<grid, 256, 0, s>>>((OT*)out, (const AT*)a, (const WT*)w, M, N, K, lda, ldo,  \
+                                                            a_head, o_head)
+    if (a_dtype == DT_F32 && w_dtype == DT_F32 && out_dtype == DT_F32) { MLLM_HEAD_LINEAR(float, float, float); }
+    else if (a_dtype == DT_BF16 && w_dtype == DT_BF16 && out_dtype == DT_F32) { MLLM_HEAD_LINEAR(bf16, bf16, float); }
+    else if (a_dtype == DT_F32 && w_dtype == DT_BF16 && out_dtype == DT_BF16) { MLLM_HEAD_LINEAR(float, bf16, bf16); }
+    else if (a_dtype == DT_BF16 && w_dtype == DT_BF16 && out_dtype == DT_BF16) { MLLM_HEAD_LINEAR(bf16, bf16, bf16); }
     else return fail("head_linear: unsupported combination of element types");
 #undef MLLM_HEAD_LINEAR
     return check_launch("head_linear_kernel");
@@ -433,11 +471,11 @@ extern "C" int mllm_sequence_latent_attention(float* out, const float* q_eff, co
 //     rows <= 128, position of the first row, part, ...; records with part != 0 are skipped),
 //     every record is cut into pieces of TQ tokens (grid.x = records * 128 / TQ);
 //   single tokens: tiles is null, TQ = 1, grid.x = tokens, and grid.z = parts: part z takes the
-//     keys [z * keys_per_part, (z + 1) * keys_per_part) and leaves (max, sum, unnormalised result)
-//     for latent_merge_kernel.
+//     z-th run of the token's keys (its context length / parts, rounded up to whole blocks) and
+//     leaves (max, sum, unnormalised result) for latent_merge_kernel.
 // ---------------------------------------------------------------------------
 struct LatentTiledParams {
-    float* out;                    // [T, heads * rank] (parts == 1)
+    void* out;                     // [T, heads * rank], 32-bit or bfloat16
     float* part_out;               // [T, heads, parts, rank]
     float* part_ml;                // [T, heads, parts, 2]
     const float* q_eff;            // [T, heads * (rank + rot)]
@@ -445,12 +483,23 @@ struct LatentTiledParams {
     const int* block_table; const int* positions; const int* token_item; const int* tiles;
     int max_blocks, page_size, n_tokens, heads, rank, rot, TQ, HB, parts, keys_per_part;
     float scale;
+    int out_bf16;                  // `out` holds bfloat16 (the expansion that follows then runs on the tensor cores)
+    int key_buffers;               // 2: the next block of cached rows is copied (cp.async) while this one is used; 1: no room for that
 };
 
 template <typename T> struct Chunk4;
 template <> struct Chunk4<float> { typedef float4 type; };
 template <> struct Chunk4<bf16> { typedef uint2 type; };
 __device__ __forceinline__ void unpack4(const float4& c, float* v) { v[0] = c.x; v[1] = c.y; v[2] = c.z; v[3] = c.w; }
+// An asynchronous copy of BYTES (8 or 16) to shared memory; with `real` false nothing is read and zeros are written.
+template <int BYTES>
+__device__ __forceinline__ void copy_async(void* to_shared, const void* from_global, bool real) {
+    const unsigned to = (unsigned)__cvta_generic_to_shared(to_shared);
+    const int bytes = real ? BYTES : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], %2, %3;" ::"r"(to), "l"(from_global), "n"(BYTES), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void copies_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int LEFT> __device__ __forceinline__ void copies_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(LEFT) : "memory"); }
 __device__ __forceinline__ void unpack4(const uint2& c, float* v) {
     const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&c.x));
     const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&c.y));
@@ -492,8 +541,10 @@ latent_attention_tiled_kernel(LatentTiledParams p) {
     const int* bt = p.block_table + (long)item * p.max_blocks;
     int key_begin = 0, key_end = first_position + rows;            // keys [key_begin, key_end)
     if (p.parts > 1) {
-        key_begin = blockIdx.z * p.keys_per_part;
-        key_end = min(key_end, key_begin + p.keys_per_part);
+        // the token's own keys, cut into `parts` runs of whole blocks: nothing depends on a length the host knew
+        const int per_part = ((key_end + p.parts - 1) / p.parts + BK - 1) / BK * BK;
+        key_begin = blockIdx.z * per_part;
+        key_end = min(key_end, key_begin + per_part);
     }
     const bool empty = key_begin >= key_end;
     // row r of the block: token r / HB of the piece, head head0 + r % HB
@@ -523,21 +574,34 @@ latent_attention_tiled_kernel(LatentTiledParams p) {
     const int rg = tid / CG, cg = tid % CG;
     const int rp = tid >> 4, jp = tid & 15;
 
-    for (int k0 = key_begin; k0 < key_end; k0 += BK) {
-        __syncthreads();                                            // the block before is used up (and Qs is written)
+    T* const K_first = Ks;
+    T* const K_second = Ks + (p.key_buffers == 2 ? BK * ld : 0);
+    auto ask = [&](int k0, T* into) {
         for (int i = tid; i < BK * (row_width / 4); i += 256) {
             const int j = i / (row_width / 4), c = (i % (row_width / 4)) * 4;
             const int key = k0 + j;
-            chunk_t x;
-            memset(&x, 0, sizeof(x));
-            if (key < key_end) {
-                const T* row = reinterpret_cast<const T*>(p.pages) +
-                               ((long)bt[key / p.page_size] * p.page_size + (key % p.page_size)) * row_width;
-                x = *reinterpret_cast<const chunk_t*>(row + c);
-            }
-            *reinterpret_cast<chunk_t*>(Ks + j * ld + c) = x;
+            const bool real = key < key_end;
+            const T* row = reinterpret_cast<const T*>(p.pages);
+            if (real) row += ((long)bt[key / p.page_size] * p.page_size + (key % p.page_size)) * row_width + c;
+            copy_async<(int)sizeof(chunk_t)>(into + j * ld + c, row, real);
         }
-        __syncthreads();
+        copies_commit();
+    };
+    if (p.key_buffers == 2 && !empty) ask(key_begin, K_first);
+    int turn = 0;
+    for (int k0 = key_begin; k0 < key_end; k0 += BK, turn ^= 1) {
+        if (p.key_buffers == 2) {
+            Ks = turn ? K_second : K_first;
+            // (the block after this one goes where the block before it lay: the barrier that ended the last round freed it)
+            if (k0 + BK < key_end) ask(k0 + BK, turn ? K_first : K_second);
+            else copies_commit();
+            copies_wait<1>();
+        } else {
+            __syncthreads();                                        // the block before is used up
+            ask(k0, Ks);
+            copies_wait<0>();
+        }
+        __syncthreads();                                            // (Qs and row_position are written, too)
         // scores: rows rp, rp + 16 against keys jp, jp + 16
         {
             float s00 = 0.0f, s01 = 0.0f, s10 = 0.0f, s11 = 0.0f;
@@ -601,6 +665,7 @@ latent_attention_tiled_kernel(LatentTiledParams p) {
                 }
             }
         }
+        if (p.key_buffers == 2) __syncthreads();                    // this block is used up: the next round may overwrite it
     }
     __syncthreads();
     if (lane == 0) {
@@ -627,9 +692,15 @@ latent_attention_tiled_kernel(LatentTiledParams p) {
                 for (int x = 0; x < 8; x++) o[x] = empty ? 0.0f : acc[i][ct * 8 + x];
             } else {
                 const float inv = 1.0f / sums[r];
-                float* o = p.out + at * p.rank + c0;
+                if (p.out_bf16) {
+                    bf16* o = reinterpret_cast<bf16*>(p.out) + at * p.rank + c0;
 #pragma unroll
-                for (int x = 0; x < 8; x++) o[x] = acc[i][ct * 8 + x] * inv;
+                    for (int x = 0; x < 8; x++) o[x] = __float2bfloat16_rn(acc[i][ct * 8 + x] * inv);
+                } else {
+                    float* o = reinterpret_cast<float*>(p.out) + at * p.rank + c0;
+#pragma unroll
+                    for (int x = 0; x < 8; x++) o[x] = acc[i][ct * 8 + x] * inv;
+                }
             }
         }
         if (p.parts > 1 && cg == 0) {
@@ -640,7 +711,7 @@ latent_attention_tiled_kernel(LatentTiledParams p) {
 }
 
 // The parts of a (token, head) into one result, in the order of the parts.
-__global__ void latent_merge_kernel(float* __restrict__ out, const float* __restrict__ part_out,
+__global__ void latent_merge_kernel(void* __restrict__ out, int out_bf16, const float* __restrict__ part_out,
                                     const float* __restrict__ part_ml, int parts, int rank) {
     const long at = blockIdx.x;
     const float* ml = part_ml + at * parts * 2;
@@ -653,13 +724,14 @@ __global__ void latent_merge_kernel(float* __restrict__ out, const float* __rest
         float o = 0.0f;
         for (int z = 0; z < parts; z++)
             if (ml[2 * z] != -INFINITY) o = fmaf(part_out[(at * parts + z) * rank + d], expf(ml[2 * z] - big), o);
-        out[at * rank + d] = o / total;
+        if (out_bf16) reinterpret_cast<bf16*>(out)[at * rank + d] = __float2bfloat16_rn(o / total);
+        else reinterpret_cast<float*>(out)[at * rank + d] = o / total;
     }
 }
 
-static size_t latent_tiled_shared_bytes(int row_width, int element_bytes) {
+static size_t latent_tiled_shared_bytes(int row_width, int element_bytes, int key_buffers) {
     const size_t ld = (size_t)row_width + 4;
-    return 32 * ld * 4 + 32 * 33 * 4 + 64 * 4 + 32 * ld * (size_t)element_bytes;
+    return 32 * ld * 4 + 32 * 33 * 4 + 64 * 4 + key_buffers * 32 * ld * (size_t)element_bytes;
 }
 
 template <typename T, int RPT, int CT>
@@ -686,9 +758,11 @@ extern "C" int mllm_sequence_latent_attention_tiled(const LatentTiledParams* par
     if (row_width % 4 != 0 || p.rank % 8 != 0 || p.rank > 1024) return fail("latent_attention_tiled: the row must be a multiple of 4 and the latent of 8, at most 1024");
     if (p.HB <= 0 || p.TQ <= 0 || p.HB * p.TQ != 32 || 128 % p.TQ != 0) return fail("latent_attention_tiled: a block takes 32 rows");
     if (p.tiles == nullptr && p.TQ != 1) return fail("latent_attention_tiled: single tokens come one per block");
-    if (p.parts < 1 || (p.parts > 1 && (p.tiles != nullptr || p.keys_per_part <= 0 || p.part_out == nullptr || p.part_ml == nullptr)))
+    if (p.parts < 1 || (p.parts > 1 && (p.tiles != nullptr || p.part_out == nullptr || p.part_ml == nullptr)))
         return fail("latent_attention_tiled: parts are for single tokens and need scratch");
-    const size_t shared = latent_tiled_shared_bytes(row_width, dtype == DT_F32 ? 4 : 2);
+    const int element_bytes = dtype == DT_F32 ? 4 : 2;
+    p.key_buffers = latent_tiled_shared_bytes(row_width, element_bytes, 2) <= 220 * 1024 ? 2 : 1;
+    const size_t shared = latent_tiled_shared_bytes(row_width, element_bytes, p.key_buffers);
     if (shared > 220 * 1024) return fail("latent_attention_tiled: the rows do not fit in shared memory");
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(p.tiles != nullptr ? n_units * (128 / p.TQ) : n_units, (p.heads + p.HB - 1) / p.HB, p.parts);
@@ -697,7 +771,7 @@ extern "C" int mllm_sequence_latent_attention_tiled(const LatentTiledParams* par
     else if (dtype == DT_BF16) rc = pick_latent_tiled<bf16>(p, grid, shared, s);
     else return fail("latent_attention_tiled: unknown dtype");
     if (rc != 0 || p.parts == 1) return rc;
-    latent_merge_kernel<<<(unsigned)((long)n_units * p.heads), 128, 0, s>>>(p.out, p.part_out, p.part_ml, p.parts, p.rank);
+    latent_merge_kernel<<<(unsigned)((long)n_units * p.heads), 128, 0, s>>>(p.out, p.out_bf16, p.part_out, p.part_ml, p.parts, p.rank);
     return check_launch("latent_merge_kernel");
 }
 
@@ -904,10 +978,69 @@ memory_chunk_kernel(MemoryScanParams p) {
     const T* k = (const T*)p.k + (long)head * dim;
     const T* v = (const T*)p.v + (long)head * vdim;
     const int t_mine = tid >> 3, vg = tid & 7;
+    // Rows of q, k and v come as 16-byte vectors where the sizes allow it, and the next chunk's are
+    // asked for before this chunk is computed, so that their way from memory lies under the sums.
+    constexpr int VEC = 16 / (int)sizeof(T), MAXV = 4;
+    const int n_vec = dim / VEC;
+    const bool vectors = dim % VEC == 0 && vdim % VEC == 0 && p.ld_q % VEC == 0 && p.ld_k % VEC == 0 && p.ld_v % VEC == 0 &&
+                         (reinterpret_cast<uintptr_t>(p.q) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.k) & 15) == 0 &&
+                         (reinterpret_cast<uintptr_t>(p.v) & 15) == 0 && C * n_vec <= 256 * MAXV;
+    uint4 q_next[MAXV], k_next[MAXV], v_next;
+    auto ask = [&](int done) {
+        const int n = min(C, count - done);
+        const long row0 = first + done;
+        const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int e = 0; e < MAXV; e++) {
+            const int i = tid + e * 256, t = i / n_vec, c = (i % n_vec) * VEC;
+            const bool there = i < C * n_vec && t < n;
+            q_next[e] = there ? *reinterpret_cast<const uint4*>(q + (row0 + t) * p.ld_q + c) : zero;
+            k_next[e] = there ? *reinterpret_cast<const uint4*>(k + (row0 + t) * p.ld_k + c) : zero;
+        }
+        const int t = tid / (VS / VEC), c = (tid % (VS / VEC)) * VEC;
+        v_next = (t < n && v0 + c < vdim) ? *reinterpret_cast<const uint4*>(v + (row0 + t) * p.ld_v + v0 + c) : zero;
+    };
+    auto unpack = [](const uint4& x, float* out) {
+        if (sizeof(T) == 4) {
+            out[0] = __uint_as_float(x.x); out[1] = __uint_as_float(x.y); out[2] = __uint_as_float(x.z); out[3] = __uint_as_float(x.w);
+        } else {
+            const unsigned parts[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float2 two = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&parts[j]));
+                out[2 * j] = two.x;
+                out[2 * j + 1] = two.y;
+            }
+        }
+    };
+    if (vectors) ask(0);
     for (int done = 0; done < count; done += C) {
         const int n = min(C, count - done), last = n - 1;
         const long row0 = first + done;
         __syncthreads();                  // the chunk before is done with everything
+        if (vectors) {
+#pragma unroll
+            for (int e = 0; e < MAXV; e++) {
+                const int i = tid + e * 256, t = i / n_vec, c = (i % n_vec) * VEC;
+                if (i < C * n_vec) {
+                    float qx[VEC], kx[VEC];
+                    unpack(q_next[e], qx);
+                    unpack(k_next[e], kx);
+#pragma unroll
+                    for (int x = 0; x < VEC; x++) {
+                        qs[t * ldq + c + x] = (p.silu ? silu_f(qx[x]) : qx[x]) * p.q_scale;
+                        ks[t * ldq + c + x] = p.silu ? silu_f(kx[x]) : kx[x];
+                    }
+                }
+            }
+            if (tid < C * (VS / VEC)) {
+                float vx[VEC];
+                unpack(v_next, vx);
+#pragma unroll
+                for (int x = 0; x < VEC; x++) vs[tid * VEC + x] = p.silu ? silu_f(vx[x]) : vx[x];
+            }
+            if (done + C < count) ask(done + C);
+        } else {
         for (int i = tid; i < C * dimp; i += 256) {
             const int t = i / dimp, d = i % dimp;
             float qd = 0.0f, kd = 0.0f;
@@ -928,6 +1061,7 @@ memory_chunk_kernel(MemoryScanParams p) {
             float x = (t < n && c < vdim) ? to_f32(v[(row0 + t) * p.ld_v + c]) : 0.0f;
             if (p.silu) x = silu_f(x);
             vs[i] = x;
+        }
         }
         if (gated && warp == 0) {
             float lf = 0.0f, li = -INFINITY;
@@ -1099,6 +1233,402 @@ extern "C" int mllm_sequence_memory_chunk(const MemoryScanParams* params, int n_
         return fail("memory_chunk: unknown dtype");
     }
     return check_launch("memory_chunk_kernel");
+}
+
+// ---------------------------------------------------------------------------
+// The chunked recurrence with the chunks side by side.  What ties a chunk to the one before it
+// is only the state it starts from, and that follows from the chunks' own sums by a short scan:
+//   gates   (gated kind) one warp per (entry, head) walks the entry's gates and leaves, per token:
+//           b, M, F, the weight of the carried state, and the token's weight in its chunk's sum
+//   sums    per (chunk, head, slice), all at once: D = sum_s weight[last, s] k_s v_s^T  (and of k alone)
+//   scan    per (entry, head, slice): S_before(chunk) = S;  S <- carried weight(chunk) S + D(chunk);
+//           the chunk's slot in scratch then holds S_before; the entry's state is written at the end
+//   read    per (chunk, head, slice), all at once: the scores and outputs of memory_chunk_kernel,
+//           from S_before
+// Chunks are numbered through the step: entry i owns ceil(count_i / 32) of them; a block finds its
+// chunk by walking the entries' counts, so the grid depends on the step's shape only
+// (tokens / 32 + entries blocks; those beyond the last chunk leave at once).
+// ---------------------------------------------------------------------------
+struct MemoryPassParams {
+    MemoryScanParams base;
+    float* gate_arrays;            // [T, heads, 5]
+    float* chunk_state;            // [chunks, heads, dim, vdim]
+    float* chunk_norm;             // [chunks, heads, dim]
+    int max_chunks, n_items;
+};
+
+__device__ __forceinline__ bool find_chunk(const int* __restrict__ item_count, int n_items, int chunk, int& item, int& local) {
+    int before = 0;
+    for (int i = 0; i < n_items; i++) {
+        const int mine = (item_count[i] + 31) >> 5;
+        if (chunk < before + mine) {
+            item = i;
+            local = chunk - before;
+            return true;
+        }
+        before += mine;
+    }
+    return false;
+}
+
+__global__ void __launch_bounds__(32) memory_gates_kernel(MemoryPassParams pp) {
+    const MemoryScanParams& p = pp.base;
+    const int item = blockIdx.x, head = blockIdx.y, lane = threadIdx.x, heads = p.heads;
+    const int count = p.item_count[item];
+    if (count <= 0) return;
+    float* m_held = p.state + (long)p.item_slot[item] * p.state_stride + (long)heads * p.dim * p.vdim + (long)heads * p.dim + head;
+    float m_before = *m_held;
+    const long first = p.item_offset[item];
+    for (int done = 0; done < count; done += 32) {
+        const int n = min(32, count - done), last = n - 1;
+        const long row = first + done + lane;
+        float lf = 0.0f, li = -INFINITY;
+        if (lane < n) {
+            const float gi = p.gates[row * p.ld_gates + head] + p.gate_bias[head];
+            const float gf = p.gates[row * p.ld_gates + heads + head] + p.gate_bias[heads + head];
+            li = p.gate_cap * tanhf(gi / p.gate_cap);
+            lf = log_sigmoid_f(p.gate_cap * tanhf(gf / p.gate_cap));
+        }
+        float F = lf;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float up = __shfl_up_sync(0xffffffffu, F, o);
+            if (lane >= o) F += up;
+        }
+        const float b = li - F;
+        float M = b;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float up = __shfl_up_sync(0xffffffffu, M, o);
+            if (lane >= o) M = fmaxf(M, up);
+        }
+        M = fmaxf(M, m_before);
+        const float M_last = __shfl_sync(0xffffffffu, M, last), F_last = __shfl_sync(0xffffffffu, F, last);
+        if (lane < n) {
+            float* mine = pp.gate_arrays + (row * heads + head) * 5;
+            mine[0] = b;
+            mine[1] = M;
+            mine[2] = F;
+            mine[3] = expf(m_before - M);
+            mine[4] = expf(b - M_last);
+        }
+        m_before = F_last + M_last;
+    }
+    if (p.writes && lane == 0) *m_held = m_before;
+}
+
+// What a block of the passes over chunks shares: where its chunk lies.
+struct ChunkPlace {
+    int item, local, n, chunk;
+    long row0;
+};
+__device__ __forceinline__ bool place_chunk(const MemoryPassParams& pp, ChunkPlace& at) {
+    at.chunk = blockIdx.x;
+    if (!find_chunk(pp.base.item_count, pp.n_items, at.chunk, at.item, at.local)) return false;
+    at.n = min(32, pp.base.item_count[at.item] - at.local * 32);
+    at.row0 = (long)pp.base.item_offset[at.item] + at.local * 32;
+    return true;
+}
+
+template <typename T>
+__device__ __forceinline__ void load_chunk_rows(const MemoryScanParams& p, const ChunkPlace& at, int head, int v0, float* qs,
+                                                float* ks, float* vs, int ldq, int dimp) {
+    const T* q = (const T*)p.q + (long)head * p.dim;
+    const T* k = (const T*)p.k + (long)head * p.dim;
+    const T* v = (const T*)p.v + (long)head * p.vdim;
+    for (int i = threadIdx.x; i < 32 * dimp; i += 256) {
+        const int t = i / dimp, d = i % dimp;
+        float qd = 0.0f, kd = 0.0f;
+        if (t < at.n && d < p.dim) {
+            if (qs != nullptr) qd = to_f32(q[(at.row0 + t) * p.ld_q + d]);
+            kd = to_f32(k[(at.row0 + t) * p.ld_k + d]);
+            if (p.silu) {
+                qd = silu_f(qd);
+                kd = silu_f(kd);
+            }
+            qd *= p.q_scale;
+        }
+        if (qs != nullptr) qs[t * ldq + d] = qd;
+        ks[t * ldq + d] = kd;
+    }
+    for (int i = threadIdx.x; i < 32 * 32; i += 256) {
+        const int t = i / 32, c = v0 + (i % 32);
+        float x = (t < at.n && c < p.vdim) ? to_f32(v[(at.row0 + t) * p.ld_v + c]) : 0.0f;
+        if (p.silu) x = silu_f(x);
+        vs[i] = x;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) memory_sums_kernel(MemoryPassParams pp) {
+    const MemoryScanParams& p = pp.base;
+    ChunkPlace at;
+    if (!place_chunk(pp, at)) return;
+    extern __shared__ __align__(16) float shared[];
+    const int head = blockIdx.y, v0 = blockIdx.z * 32, tid = threadIdx.x, heads = p.heads, dim = p.dim, vdim = p.vdim;
+    const int dimp = (dim + 3) & ~3, ldq = dimp + 4, last = at.n - 1;
+    const bool gated = p.gates != nullptr;
+    float* ks = shared;                    // [32][ldq]
+    float* vs = ks + 32 * ldq;             // [32][32]
+    float* dl = vs + 32 * 32;              // [32]
+    load_chunk_rows<T>(p, at, head, v0, nullptr, ks, vs, ldq, dimp);
+    if (tid < 32) {
+        float weight = 0.0f;
+        if (tid <= last) {
+            if (gated) weight = pp.gate_arrays[((at.row0 + tid) * heads + head) * 5 + 4];
+            else {
+                weight = 1.0f;
+                for (int i = 0; i < last - tid; i++) weight *= p.decay[head];
+            }
+        }
+        dl[tid] = weight;
+    }
+    __syncthreads();
+    const int t_mine = tid >> 3, vg = tid & 7;
+    float* into = pp.chunk_state + ((long)at.chunk * heads + head) * dim * vdim;
+    for (int d = t_mine; d < dim; d += 32) {
+        float4 s4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int s_at = 0; s_at < at.n; s_at++) {
+            const float kd = ks[s_at * ldq + d] * dl[s_at];
+            const float4 v4 = *reinterpret_cast<const float4*>(vs + s_at * 32 + vg * 4);
+            s4.x = fmaf(kd, v4.x, s4.x);
+            s4.y = fmaf(kd, v4.y, s4.y);
+            s4.z = fmaf(kd, v4.z, s4.z);
+            s4.w = fmaf(kd, v4.w, s4.w);
+        }
+        const float out4[4] = {s4.x, s4.y, s4.z, s4.w};
+        for (int x = 0; x < 4; x++)
+            if (v0 + vg * 4 + x < vdim) into[(long)d * vdim + v0 + vg * 4 + x] = out4[x];
+    }
+    if (gated && blockIdx.z == 0)
+        for (int d = tid; d < dim; d += 256) {
+            float x = 0.0f;
+            for (int s_at = 0; s_at < at.n; s_at++) x = fmaf(dl[s_at], ks[s_at * ldq + d], x);
+            pp.chunk_norm[((long)at.chunk * heads + head) * dim + d] = x;
+        }
+}
+
+__global__ void __launch_bounds__(256) memory_carry_kernel(MemoryPassParams pp) {
+    const MemoryScanParams& p = pp.base;
+    const int item = blockIdx.x, head = blockIdx.y, v0 = blockIdx.z * 32, tid = threadIdx.x;
+    const int heads = p.heads, dim = p.dim, vdim = p.vdim;
+    const int count = p.item_count[item];
+    if (count <= 0) return;
+    const bool gated = p.gates != nullptr;
+    int chunk = 0;
+    for (int i = 0; i < item; i++) chunk += (p.item_count[i] + 31) >> 5;
+    const int n_chunks = (count + 31) >> 5;
+    float* held = p.state + (long)p.item_slot[item] * p.state_stride;
+    float* S_held = held + (long)head * dim * vdim;
+    float* n_held = held + (long)heads * dim * vdim + (long)head * dim;
+    const long first = p.item_offset[item];
+    const int column = v0 + (tid & 31);
+    const bool active = column < vdim;
+    // a thread owns the entries (d, column) with d = tid / 32 + 8 e
+    for (int d0 = tid >> 5; d0 < dim; d0 += 8 * 8) {
+        float S[8], delta[8];
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            const int d = d0 + 8 * e;
+            S[e] = (active && d < dim) ? S_held[(long)d * vdim + column] : 0.0f;
+        }
+        for (int c = 0; c < n_chunks; c++) {
+            const int n = min(32, count - c * 32);
+            float carried;
+            if (gated) carried = pp.gate_arrays[((first + c * 32 + n - 1) * heads + head) * 5 + 3];
+            else {
+                carried = 1.0f;
+                for (int i = 0; i < n; i++) carried *= p.decay[head];
+            }
+            float* slot = pp.chunk_state + ((long)(chunk + c) * heads + head) * dim * vdim;
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                const int d = d0 + 8 * e;
+                delta[e] = (active && d < dim) ? slot[(long)d * vdim + column] : 0.0f;
+            }
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                const int d = d0 + 8 * e;
+                if (active && d < dim) slot[(long)d * vdim + column] = S[e];
+                S[e] = fmaf(carried, S[e], delta[e]);
+            }
+        }
+        if (p.writes) {
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                const int d = d0 + 8 * e;
+                if (active && d < dim) S_held[(long)d * vdim + column] = S[e];
+            }
+        }
+    }
+    if (gated && blockIdx.z == 0) {
+        for (int d = tid; d < dim; d += 256) {
+            float x = n_held[d];
+            for (int c = 0; c < n_chunks; c++) {
+                const int n = min(32, count - c * 32);
+                const float carried = pp.gate_arrays[((first + c * 32 + n - 1) * heads + head) * 5 + 3];
+                float* slot = pp.chunk_norm + ((long)(chunk + c) * heads + head) * dim + d;
+                const float delta = *slot;
+                *slot = x;
+                x = fmaf(carried, x, delta);
+            }
+            if (p.writes) n_held[d] = x;
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) memory_read_kernel(MemoryPassParams pp) {
+    const MemoryScanParams& p = pp.base;
+    ChunkPlace at;
+    if (!place_chunk(pp, at)) return;
+    constexpr int C = 32, VS = 32;
+    extern __shared__ __align__(16) float shared[];
+    const int head = blockIdx.y, v0 = blockIdx.z * VS, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int heads = p.heads, dim = p.dim, vdim = p.vdim;
+    const int dimp = (dim + 3) & ~3, ldq = dimp + 4, n = at.n;
+    const bool gated = p.gates != nullptr;
+    float* qs = shared;                   // [C][ldq]
+    float* ks = qs + C * ldq;             // [C][ldq]
+    float* vs = ks + C * ldq;             // [C][VS]
+    float* S = vs + C * VS;               // [dimp][VS]
+    float* A = S + dimp * VS;             // [C][C + 4]
+    float* nv = A + C * (C + 4);          // [dimp]
+    float* bs = nv + dimp;                // [C]
+    float* Mt = bs + C;                   // [C]
+    float* Fs = Mt + C;                   // [C]
+    float* wt = Fs + C;                   // [C]
+    float* nq = wt + C;                   // [C]
+    float* pw = nq + C;                   // [C + 1]
+    load_chunk_rows<T>(p, at, head, v0, qs, ks, vs, ldq, dimp);
+    const float* before = pp.chunk_state + ((long)at.chunk * heads + head) * dim * vdim;
+    for (int i = tid; i < dimp * VS; i += 256) {
+        const int d = i / VS, c = v0 + (i % VS);
+        S[i] = (d < dim && c < vdim) ? before[(long)d * vdim + c] : 0.0f;
+    }
+    for (int d = tid; d < dimp; d += 256)
+        nv[d] = (gated && d < dim) ? pp.chunk_norm[((long)at.chunk * heads + head) * dim + d] : 0.0f;
+    if (warp == 0) {
+        if (gated) {
+            const float* mine = pp.gate_arrays + ((at.row0 + lane) * heads + head) * 5;
+            const bool there = lane < n;
+            bs[lane] = there ? mine[0] : -INFINITY;
+            Mt[lane] = there ? mine[1] : 0.0f;
+            Fs[lane] = there ? mine[2] : 0.0f;
+            wt[lane] = there ? mine[3] : 0.0f;
+        } else if (lane == 0) {
+            float power = 1.0f;
+            for (int i = 0; i <= C; i++) {
+                pw[i] = power;
+                power *= p.decay[head];
+            }
+        }
+    }
+    __syncthreads();
+    if (!gated && warp == 0) wt[lane] = pw[lane + 1];
+    const int t_mine = tid >> 3, vg = tid & 7;
+    {
+        const int sg = tid & 7;
+        float dot[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int d = 0; d < dimp; d += 4) {
+            const float4 q4 = *reinterpret_cast<const float4*>(qs + t_mine * ldq + d);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float4 k4 = *reinterpret_cast<const float4*>(ks + (sg + 8 * i) * ldq + d);
+                dot[i] = fmaf(q4.x, k4.x, fmaf(q4.y, k4.y, fmaf(q4.z, k4.z, fmaf(q4.w, k4.w, dot[i]))));
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int s_at = sg + 8 * i;
+            float weight = 0.0f;
+            if (s_at <= t_mine && s_at < n && t_mine < n) weight = gated ? expf(bs[s_at] - Mt[t_mine]) : pw[t_mine - s_at];
+            A[t_mine * (C + 4) + s_at] = dot[i] * weight;
+        }
+        if (gated) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int t = warp * 4 + i;
+                float part = 0.0f;
+                for (int d = lane; d < dimp; d += 32) part = fmaf(nv[d], qs[t * ldq + d], part);
+                part = warp_sum(part);
+                if (lane == 0) nq[t] = part;
+            }
+        }
+    }
+    __syncthreads();
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int d = 0; d < dimp; d += 4) {
+        const float4 q4 = *reinterpret_cast<const float4*>(qs + t_mine * ldq + d);
+        const float qd[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float4 s4 = *reinterpret_cast<const float4*>(S + (d + i) * VS + vg * 4);
+            acc.x = fmaf(qd[i], s4.x, acc.x);
+            acc.y = fmaf(qd[i], s4.y, acc.y);
+            acc.z = fmaf(qd[i], s4.z, acc.z);
+            acc.w = fmaf(qd[i], s4.w, acc.w);
+        }
+    }
+    const float carried = wt[t_mine];
+    acc.x *= carried; acc.y *= carried; acc.z *= carried; acc.w *= carried;
+    float row_sum = 0.0f;
+    for (int s_at = 0; s_at <= t_mine; s_at++) {
+        const float a = A[t_mine * (C + 4) + s_at];
+        const float4 v4 = *reinterpret_cast<const float4*>(vs + s_at * VS + vg * 4);
+        acc.x = fmaf(a, v4.x, acc.x);
+        acc.y = fmaf(a, v4.y, acc.y);
+        acc.z = fmaf(a, v4.z, acc.z);
+        acc.w = fmaf(a, v4.w, acc.w);
+        row_sum += a;
+    }
+    if (gated) {
+        const float below = fmaxf(fabsf(fmaf(carried, nq[t_mine], row_sum)), expf(-(Fs[t_mine] + Mt[t_mine]))) + 1e-6f;
+        acc.x /= below; acc.y /= below; acc.z /= below; acc.w /= below;
+    }
+    if (t_mine < n) {
+        float* o = p.out + (at.row0 + t_mine) * p.ld_out + (long)head * vdim + v0 + vg * 4;
+        const int left = vdim - (v0 + vg * 4);
+        if (left > 0) o[0] = acc.x;
+        if (left > 1) o[1] = acc.y;
+        if (left > 2) o[2] = acc.z;
+        if (left > 3) o[3] = acc.w;
+    }
+}
+
+// Scratch the passes need, in floats: gate arrays, chunk states, chunk norms.
+extern "C" int mllm_sequence_memory_passes(const MemoryPassParams* params, int dtype, void* stream) {
+    MemoryPassParams pp = *params;
+    const MemoryScanParams& p = pp.base;
+    if (pp.n_items <= 0 || pp.max_chunks <= 0) return 0;
+    if (p.heads <= 0 || p.heads > 65535 || p.dim <= 0 || p.vdim <= 0) return fail("memory_passes: bad sizes");
+    const size_t shared = memory_chunk_shared_bytes(p.dim);
+    if (shared > 200 * 1024) return fail("memory_passes: the key size is too large for a chunk in shared memory");
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool gated = p.gates != nullptr;
+    const int slices = (p.vdim + 31) / 32;
+    if (gated) memory_gates_kernel<<<dim3(pp.n_items, p.heads), 32, 0, s>>>(pp);
+    dim3 over_chunks(pp.max_chunks, p.heads, slices), over_items(pp.n_items, p.heads, slices);
+    if (dtype == DT_F32) {
+        if (shared > 48 * 1024) {
+            cudaFuncSetAttribute(memory_sums_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+            cudaFuncSetAttribute(memory_read_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        }
+        memory_sums_kernel<float><<<over_chunks, 256, shared, s>>>(pp);
+        memory_carry_kernel<<<over_items, 256, 0, s>>>(pp);
+        memory_read_kernel<float><<<over_chunks, 256, shared, s>>>(pp);
+    } else if (dtype == DT_BF16) {
+        if (shared > 48 * 1024) {
+            cudaFuncSetAttribute(memory_sums_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+            cudaFuncSetAttribute(memory_read_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        }
+        memory_sums_kernel<bf16><<<over_chunks, 256, shared, s>>>(pp);
+        memory_carry_kernel<<<over_items, 256, 0, s>>>(pp);
+        memory_read_kernel<bf16><<<over_chunks, 256, shared, s>>>(pp);
+    } else {
+        return fail("memory_passes: unknown dtype");
+    }
+    return check_launch("memory_passes");
 }
 
 // ---------------------------------------------------------------------------

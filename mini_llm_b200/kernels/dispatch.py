@@ -106,9 +106,29 @@ class Kernels:
         return ops.latent_prepare(cache.k_pages, q_eff, down, q, gain, inv_freq, ctx.positions, ctx.token_item,
                                   cache.block_table, cache.page_size, rank, rot, rot_dims, heads, dim, eps, cache.writes)
 
-    def head_linear(self, out, a, w, heads, a_head, o_head):
+    HEAD_LINEAR_GEMM_ROWS = 128   # from here on each head's product goes to the tensor-core kernel by itself
+
+    def head_linear(self, ctx, out, a, w, heads, a_head, o_head):
+        m, n, k = a.shape[0], w.shape[1], w.shape[2]
+        if (not self.plain_only and m >= self.HEAD_LINEAR_GEMM_ROWS and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+                and n >= 16 and all(ops.gemm_takes(a[:, h * a_head:h * a_head + k], w[h]) for h in (0, heads - 1))
+                and (a_head * 2) % 16 == 0):
+            # prompt portions: one launch per head (strided views of a and out; no copy)
+            self.launches += heads
+            self.chose("head_linear", "gemm_tcgen05", m, n, k, heads)
+            status = self.status(ctx.device)
+            for h in range(heads):
+                ops.gemm_bf16(out[:, h * o_head:h * o_head + n], a[:, h * a_head:h * a_head + k], w[h], None, "store", status)
+            return out
         self.launches += 1
+        self.chose("head_linear", "head_linear_plain", m, n, k, heads)
         return ops.head_linear(out, a, w, heads, a_head, o_head)
+
+    def latent_mixed_dtype(self, cache, rank, rot):
+        """The element type attention over a latent hands its result on in: bfloat16 where the tiled
+        kernel runs (the expansion per head then takes the tensor cores), else 32-bit."""
+        tiled = not self.plain_only and ops.latent_attention_tiled_takes(cache.k_pages, rank, rot)
+        return torch.bfloat16 if tiled and self.act_dtype == torch.bfloat16 else torch.float32
 
     def latent_attention(self, ctx, out, q_eff, cache, heads, rank, rot, scale):
         self.launches += 1
@@ -123,17 +143,19 @@ class Kernels:
             if ctx.decode_only:
                 # single tokens: all heads of a token share the cached rows; while the (token, head
                 # block) pairs are fewer than twice the SMs, each token's keys come in parts
-                reach = cache.block_table.shape[1] * cache.page_size
                 blocks = n * -(-heads // ops.LATENT_TILE_ROWS)
-                parts = max(1, min(32, 296 // blocks, -(-reach // 64)))
-                per_part = -(-(-(-reach // parts)) // 32) * 32
+                parts = max(1, min(32, 296 // blocks))
                 scratch = self._latent_scratch(ctx.device, n * heads * parts * rank, n * heads * parts * 2) if parts > 1 else None
                 self.launches += 1 if parts > 1 else 0
                 self.chose("latent_attention", "latent_attention_tiled_parts", n, heads, rank + rot)
-                return ops.latent_attention_tiled(*common, parts=parts, keys_per_part=per_part, scratch=scratch)
+                return ops.latent_attention_tiled(*common, parts=parts, scratch=scratch)
         self.chose("latent_attention", "latent_attention_plain", n, heads, rank + rot)
-        return ops.latent_attention_plain(out, q_eff, cache.k_pages, cache.block_table, ctx.positions, ctx.token_item,
-                                          heads, rank, rot, cache.page_size, scale)
+        plain_out = out if out.dtype == torch.float32 else ctx.buffer("latent_mixed_32", out.shape, torch.float32)
+        ops.latent_attention_plain(plain_out, q_eff, cache.k_pages, cache.block_table, ctx.positions, ctx.token_item,
+                                   heads, rank, rot, cache.page_size, scale)
+        if plain_out is not out:
+            out.copy_(plain_out)
+        return out
 
     def memory_scan(self, ctx, out, q, k, v, state, heads, dim, vdim, writes=True, **how):
         self.launches += 1
@@ -181,8 +203,8 @@ class Kernels:
         m, k = a.shape
         self.launches += 1
         # activations the fast kernels do not apply, and products too narrow for a tile, go to the plain kernel
-        fast = epilogue in ops.GEMM_EPILOGUES and w.shape[0] >= 16
-        skinny = fast and self._skinny(m, k, w.shape[0])
+        fast = w.shape[0] >= 16                  # (a product narrower than a tile's smallest box goes to the plain kernel)
+        skinny = self._skinny(m, k, w.shape[0])
         deferred = isinstance(a, DeferredNorm)
         if deferred and not (skinny and a.kind in self.FUSED_NORM_KINDS):
             a, deferred = a.materialize(ctx), False      # no kernel here norms this kind on the way in: the norm runs first

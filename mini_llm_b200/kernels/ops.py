@@ -918,7 +918,7 @@ class _LatentTiledParams(ctypes.Structure):
     _fields_ = [("out", P), ("part_out", P), ("part_ml", P), ("q_eff", P), ("pages", P), ("block_table", P),
                 ("positions", P), ("token_item", P), ("tiles", P), ("max_blocks", I), ("page_size", I), ("n_tokens", I),
                 ("heads", I), ("rank", I), ("rot", I), ("TQ", I), ("HB", I), ("parts", I), ("keys_per_part", I),
-                ("scale", F)]
+                ("scale", F), ("out_bf16", I), ("key_buffers", I)]
 
 
 _latent_attention_tiled = Function("sequence", "mllm_sequence_latent_attention_tiled",
@@ -944,12 +944,15 @@ def latent_heads_per_block(heads: int) -> int:
 
 
 def latent_attention_tiled(out, q_eff, pages, block_table, positions, token_item, heads, rank, rot, page_size, scale,
-                           tiles=None, n_tiles=0, parts=1, keys_per_part=0, scratch=None):
+                           tiles=None, n_tiles=0, parts=1, scratch=None):
     """``latent_attention_plain`` in tiles of 32 query rows that share their keys.  With ``tiles``
     (the step's work list, device int32 records of 8, ``n_tiles`` of them) for prompt portions;
-    without, for single tokens, the keys of each in ``parts`` parts of ``keys_per_part`` keys whose
-    results are merged (``scratch``: fp32 (T * heads * parts * rank, T * heads * parts * 2))."""
-    _check(out, "latent_attention.out", torch.float32, 2)
+    without, for single tokens, the keys of each in ``parts`` runs (the token's context length over
+    ``parts``, in whole blocks of 32) whose results are merged (``scratch``: fp32 (T * heads * parts * rank, T * heads * parts * 2)).
+    ``out`` may be bfloat16: the sums are 32-bit either way, the result is rounded once."""
+    _check(out, "latent_attention.out", None, 2)
+    if out.dtype not in (torch.float32, torch.bfloat16):
+        raise KernelError("latent_attention_tiled: out must be float32 or bfloat16")
     _check(q_eff, "latent_attention.q_eff", torch.float32, 2)
     _check(pages, "latent_attention.pages")
     _check(block_table, "latent_attention.block_table", torch.int32, 2)
@@ -964,6 +967,7 @@ def latent_attention_tiled(out, q_eff, pages, block_table, positions, token_item
     params.block_table, params.positions, params.token_item = block_table.data_ptr(), positions.data_ptr(), token_item.data_ptr()
     params.max_blocks, params.page_size, params.n_tokens = block_table.shape[1], page_size, n
     params.heads, params.rank, params.rot, params.scale = heads, rank, rot, float(scale)
+    params.out_bf16 = int(out.dtype == torch.bfloat16)
     if tiles is not None:
         _check(tiles, "latent_attention.tiles", torch.int32)
         if tiles.numel() < ATTENTION_TILE_RECORD * n_tiles or parts != 1:
@@ -973,15 +977,13 @@ def latent_attention_tiled(out, q_eff, pages, block_table, positions, token_item
         params.TQ = LATENT_TILE_ROWS // params.HB
         params.parts, units = 1, n_tiles
     else:
-        params.HB, params.TQ, params.parts, params.keys_per_part, units = LATENT_TILE_ROWS, 1, int(parts), int(keys_per_part), n
+        params.HB, params.TQ, params.parts, units = LATENT_TILE_ROWS, 1, int(parts), n
         if parts > 1:
             part_out, part_ml = scratch
             _check(part_out, "latent_attention.scratch", torch.float32)
             _check(part_ml, "latent_attention.scratch", torch.float32)
             if part_out.numel() < n * heads * parts * rank or part_ml.numel() < n * heads * parts * 2:
                 raise KernelError("latent_attention_tiled: scratch too small")
-            if keys_per_part * parts < page_size * block_table.shape[1]:
-                raise KernelError("latent_attention_tiled: the parts do not cover the longest block table")
             params.part_out, params.part_ml = part_out.data_ptr(), part_ml.data_ptr()
     _latent_attention_tiled(ctypes.byref(params), units, dtype_code(pages.dtype), _stream())
     return out

@@ -82,11 +82,11 @@ class LatentAttention(Mixer):
         q_eff = ctx.buffer("latent_q_eff", (n, h * self.row), torch.float32)
         k.latent_prepare(ctx, cache, q_eff, down, q, self.w(self.names["norm"]), self.inv_freq, self.rank, self.rot,
                          self.rotary_dims, h, self.dim, self.eps)
-        k.head_linear(q_eff, q, self.key_up_t, h, self.dim + self.rot, self.row)
-        mixed_latent = ctx.buffer("latent_mixed", (n, h * self.rank), torch.float32)
+        k.head_linear(ctx, q_eff, q, self.key_up_t, h, self.dim + self.rot, self.row)
+        mixed_latent = ctx.buffer("latent_mixed", (n, h * self.rank), k.latent_mixed_dtype(cache, self.rank, self.rot))
         k.latent_attention(ctx, mixed_latent, q_eff, cache, h, self.rank, self.rot, self.score_scale)
         mixed = ctx.buffer("attn_out", (n, h * self.vdim), ctx.act_dtype)
-        k.head_linear(mixed, mixed_latent, self.value_up, h, self.rank, self.vdim)
+        k.head_linear(ctx, mixed, mixed_latent, self.value_up, h, self.rank, self.vdim)
         out = ctx.buffer("mixer_out", (n, self.width), torch.float32)
         k.linear(ctx, out, mixed, self.w(self.names["o"]))
         return out

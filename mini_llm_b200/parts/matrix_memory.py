@@ -123,13 +123,19 @@ class GatedMatrixMemory(MatrixMemory):
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)
         n = self.names
-        self.gate_matrix = torch.cat([self.w(n["i"]), self.w(n["f"])]).contiguous()
+        # the two gate projections as one product; rows of zeros fill it up to sixteen output
+        # features, the least the tensor-core kernel's tiles take
+        stacked = torch.cat([self.w(n["i"]), self.w(n["f"])])
+        self.gate_width = max(16, 2 * self.n_heads)
+        self.gate_matrix = torch.zeros((self.gate_width, self.width), dtype=stacked.dtype, device=stacked.device)
+        self.gate_matrix[:2 * self.n_heads] = stacked
         self.gate_bias = torch.cat([self.w(n["i_bias"]), self.w(n["f_bias"])]).contiguous()
 
     def recurrence(self, ctx, x):
-        gates = ctx.buffer("memory_gates", (x.shape[0], 2 * self.n_heads), torch.float32)
+        gates = ctx.buffer("memory_gates", (x.shape[0], self.gate_width), torch.float32)
         ctx.kernels.linear(ctx, gates, x, self.gate_matrix)
-        return dict(gates=gates, gate_bias=self.gate_bias, gate_cap=self.gate_cap, q_scale=self.dim ** -0.5)
+        return dict(gates=gates[:, :2 * self.n_heads], gate_bias=self.gate_bias, gate_cap=self.gate_cap,
+                    q_scale=self.dim ** -0.5)
 
 
 register_part("decaying_matrix_memory", DecayingMatrixMemory)

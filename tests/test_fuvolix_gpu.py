@@ -311,10 +311,9 @@ def test_latent_attention_in_tiles_against_the_plain_kernel(heads, rank, rot):
     # single tokens: the last token of each request, keys in 1, 3 and 5 parts
     last = torch.tensor([offsets[i] + new[i] - 1 for i in range(3)], device="cuda")
     for parts in (1, 3, 5):
-        per_part = -(-(-(-table.shape[1] * page_size // parts)) // 32) * 32
         scratch = (torch.empty(3 * heads * parts * rank, device="cuda"), torch.empty(3 * heads * parts * 2, device="cuda"))
         got = torch.full((3, heads * rank), float("nan"), device="cuda")
         ops.latent_attention_tiled(got, q_eff[last].contiguous(), pages, table, positions[last].contiguous(),
                                    token_item[last].contiguous(), heads, rank, rot, page_size, 0.4, parts=parts,
-                                   keys_per_part=per_part, scratch=scratch)
+                                   scratch=scratch)
         torch.testing.assert_close(got, want[last], rtol=2e-5, atol=2e-5)
