@@ -858,7 +858,8 @@ def mixer_kernels(torch, size: dict, peak: dict):
         h, dim, vdim = mem["heads"], mem["dim"], mem["vdim"]
         gated = kind == "mlstm"
         floats = ops.memory_state_floats(h, dim, vdim, gated)
-        for name, counts, chunked in (("prompts, 2 x 1024", [1024, 1024], True), ("single tokens, 8", [1] * 8, False)):
+        for name, counts, chunked in (("prompts, 2 x 1024", [1024, 1024], "passes"), ("prompts, 2 x 1024", [1024, 1024], True),
+                                      ("single tokens, 8", [1] * 8, False)):
             n = sum(counts)
             projected = [torch.randn(n, 2 * h * dim + h * vdim, device="cuda").bfloat16() for _ in range(4)]
             states = [torch.zeros(len(counts), floats, device="cuda") for _ in range(4)]
@@ -867,13 +868,20 @@ def mixer_kernels(torch, size: dict, peak: dict):
                         q_scale=dim ** -0.5) if gated else dict(decay=torch.full((h,), 0.98, device="cuda"), silu=True))
             slots, offs = dev(list(range(len(counts)))), dev([sum(counts[:i]) for i in range(len(counts))])
             cnts = dev(counts)
+            passes = None
+            if chunked == "passes":
+                passes = [torch.empty(floats, device="cuda") for floats in ops.memory_passes_scratch(n, len(counts), h, dim, vdim)]
 
             def launch(i):
                 x = projected[i % 4]
                 ops.memory_scan(out, x[:, :h * dim], x[:, h * dim:2 * h * dim], x[:, 2 * h * dim:], states[i % 4], slots, offs, cnts,
-                                h, dim, vdim, chunked=chunked, **how)
+                                h, dim, vdim, chunked=chunked is True, passes=passes, **how)
             us = replayed_us(torch, launch)
-            if chunked:
+            if chunked == "passes":
+                slices = -(-vdim // 32)
+                per_chunk = slices * 32 * 32 * dim + 32 * vdim * (dim + 16) + dim * vdim * 32
+                add(f"{kind} memory, chunks side by side, {name}", us, flops=2.0 * per_chunk * (n // 32) * h, heads=h, dim=dim, vdim=vdim)
+            elif chunked:
                 # per chunk of 32 tokens and head: 32 x 32 x dim scores (once per slice of 32 value columns),
                 # 32 x vdim x (dim + 32 / 2) for the outputs, dim x vdim x 32 for the state
                 slices = -(-vdim // 32)

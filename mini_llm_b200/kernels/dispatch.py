@@ -162,9 +162,24 @@ class Kernels:
         # prompt portions go through the kernel that takes 32 tokens at a time; a step of single
         # tokens walks each token's one update (the state is read and written once either way)
         chunked = not ctx.decode_only and ops.memory_chunk_takes(dim)
-        self.chose("memory_scan", "memory_chunk" if chunked else "memory_scan", q.shape[0], heads, dim, vdim)
+        passes = None
+        if chunked and q.shape[0] >= self.MEMORY_PASSES_TOKENS:
+            # long portions: the chunks side by side (their sums, a scan over their states, their outputs)
+            passes = self._memory_scratch(ctx.device, ops.memory_passes_scratch(q.shape[0], ctx.n_items, heads, dim, vdim))
+            self.launches += 3 if "gates" in how else 2
+        self.chose("memory_scan", "memory_passes" if passes else ("memory_chunk" if chunked else "memory_scan"),
+                   q.shape[0], heads, dim, vdim)
         return ops.memory_scan(out, q, k, v, state, ctx.item_slot, ctx.item_offset, ctx.item_count, heads, dim, vdim,
-                               writes=writes, chunked=chunked, **how)
+                               writes=writes, chunked=chunked, passes=passes, **how)
+
+    MEMORY_PASSES_TOKENS = 128     # from here on a step's chunks are worth four launches
+
+    def _memory_scratch(self, device, floats):
+        held = getattr(self, "_memory_passes", None)
+        if held is None or any(t.numel() < n for t, n in zip(held, floats)):
+            self._memory_passes = held = tuple(torch.empty(max(n, 1), dtype=torch.float32, device=device) for n in floats)
+            self.scratch_generation += 1
+        return held
 
     def depth_mix(self, hidden, kept, weights, index):
         self.launches += 1

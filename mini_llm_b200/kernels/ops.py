@@ -1000,6 +1000,20 @@ _memory_scan = Function("sequence", "mllm_sequence_memory_scan", [ctypes.POINTER
 _memory_chunk = Function("sequence", "mllm_sequence_memory_chunk", [ctypes.POINTER(_MemoryScanParams), I, I, P])
 
 
+class _MemoryPassParams(ctypes.Structure):
+    _fields_ = [("base", _MemoryScanParams), ("gate_arrays", P), ("chunk_state", P), ("chunk_norm", P), ("max_chunks", I),
+                ("n_items", I)]
+
+
+_memory_passes = Function("sequence", "mllm_sequence_memory_passes", [ctypes.POINTER(_MemoryPassParams), I, P])
+
+
+def memory_passes_scratch(n_tokens, n_items, heads, dim, vdim):
+    """Floats of scratch ``memory_scan(..., passes=...)`` needs: (gate arrays, chunk states, chunk norms)."""
+    chunks = n_tokens // 32 + n_items
+    return n_tokens * heads * 5, chunks * heads * dim * vdim, chunks * heads * dim
+
+
 def memory_chunk_takes(dim) -> bool:
     """Whether the chunked kernel takes the key size: a chunk's q and k and a slice of the state
     lie in shared memory (the launcher's own arithmetic)."""
@@ -1014,7 +1028,7 @@ def memory_state_floats(heads, dim, vdim, gated) -> int:
 
 
 def memory_scan(out, q, k, v, state, item_slot, item_offset, item_count, heads, dim, vdim, q_scale=1.0, silu=False,
-                gates=None, gate_bias=None, gate_cap=0.0, decay=None, writes=True, chunked=False):
+                gates=None, gate_bias=None, gate_cap=0.0, decay=None, writes=True, chunked=False, passes=None):
     """The matrix-memory recurrence over each entry's tokens, in order:
     S <- a S + b k v^T, out = S^T q, with a fixed decay per head (``decay`` [heads]; a = decay,
     b = 1) or with ``gates`` [T, 2 * heads] (fp32: input gates then forget gates, ``gate_bias``
@@ -1022,7 +1036,10 @@ def memory_scan(out, q, k, v, state, item_slot, item_offset, item_count, heads, 
     max(|n . q|, exp(-m)) + 1e-6.  q, k [T, heads * dim], v [T, heads * vdim] (any row stride);
     out fp32 [T, heads * vdim]; ``state`` fp32 [slots, memory_state_floats(...)].
     ``chunked``: the kernel for prompt portions, which takes 32 tokens at a time (the same sums in
-    another order); without, every token is a step of its own (single decoded tokens)."""
+    another order); without, every token is a step of its own (single decoded tokens).
+    ``passes``: three fp32 scratch tensors of ``memory_passes_scratch`` floats: the chunks are then
+    taken side by side (their own sums, a scan over the chunks' states, their outputs) instead of
+    one after the other."""
     _check(out, "memory_scan.out", torch.float32, 2)
     for name, t in (("q", q), ("k", k), ("v", v)):
         _check(t, f"memory_scan.{name}", q.dtype, 2)
@@ -1053,8 +1070,21 @@ def memory_scan(out, q, k, v, state, item_slot, item_offset, item_count, heads, 
     params.heads, params.dim, params.vdim = heads, dim, vdim
     params.q_scale, params.gate_cap = float(q_scale), float(gate_cap)
     params.silu, params.writes = int(bool(silu)), int(bool(writes))
-    if chunked and not memory_chunk_takes(dim):
-        raise KernelError(f"memory_scan: the chunked kernel does not take a key size of {dim}")
+    if (chunked or passes is not None) and not memory_chunk_takes(dim):
+        raise KernelError(f"memory_scan: the chunked kernels do not take a key size of {dim}")
+    if passes is not None:
+        n_items = item_count.shape[0]
+        need = memory_passes_scratch(n, n_items, heads, dim, vdim)
+        for t, floats in zip(passes, need):
+            _check(t, "memory_scan.passes", torch.float32, 1)
+            if t.shape[0] < floats:
+                raise KernelError("memory_scan: scratch for the passes over chunks is too small")
+        both = _MemoryPassParams()
+        both.base = params
+        both.gate_arrays, both.chunk_state, both.chunk_norm = (t.data_ptr() for t in passes)
+        both.max_chunks, both.n_items = n // 32 + n_items, n_items
+        _memory_passes(ctypes.byref(both), dtype_code(q.dtype), _stream())
+        return out
     (_memory_chunk if chunked else _memory_scan)(ctypes.byref(params), item_count.shape[0], dtype_code(q.dtype), _stream())
     return out
 

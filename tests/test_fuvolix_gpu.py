@@ -261,15 +261,18 @@ def test_memory_scan_kernel_carries_its_state():
             expected_gated[t, head] = S.T @ (qt * 0.5) / (max(abs(nv @ (qt * 0.5)), np.exp(-m)) + 1e-6)
             F = decay[head] * F + np.outer(plain.silu(kt), plain.silu(vt))
             expected_fixed[t, head] = F.T @ plain.silu(qt)
-    for gated, chunked in ((True, False), (False, False), (True, True), (False, True)):
+    for gated, chunked in ((True, False), (False, False), (True, True), (False, True), (True, "passes"), (False, "passes")):
         state = torch.zeros((2, ops.memory_state_floats(heads, dim, vdim, gated)), dtype=torch.float32, device="cuda")
         out = torch.empty((n, heads * vdim), dtype=torch.float32, device="cuda")
         for first, count in ((0, 1), (1, 9), (10, 13), (23, 32), (55, 45)):
             how = (dict(gates=dev(gates), gate_bias=dev(bias), gate_cap=cap, q_scale=0.5) if gated
                    else dict(decay=dev(decay), silu=True))
             # entry 0 is another request with no tokens in this step; entry 1 is ours, in slot 1
+            passes = None
+            if chunked == "passes":
+                passes = [torch.full((floats,), float("nan"), device="cuda") for floats in ops.memory_passes_scratch(n, 2, heads, dim, vdim)]
             ops.memory_scan(out, dev(q), dev(k), dev(v), state, dev([0, 1], torch.int32), dev([0, first], torch.int32),
-                            dev([0, count], torch.int32), heads, dim, vdim, chunked=chunked, **how)
+                            dev([0, count], torch.int32), heads, dim, vdim, chunked=chunked is True, passes=passes, **how)
         expected = (expected_gated if gated else expected_fixed).reshape(n, heads * vdim)
         # (the gates here are extreme, so n . q nearly cancels now and then, and the quotient carries the
         # sums' rounding ten times over; the chunked kernel adds in another order than the formulas above)
