@@ -1424,33 +1424,54 @@ __global__ void __launch_bounds__(256) memory_carry_kernel(MemoryPassParams pp) 
     const long first = p.item_offset[item];
     const int column = v0 + (tid & 31);
     const bool active = column < vdim;
-    // a thread owns the entries (d, column) with d = tid / 32 + 8 e
+    // a thread owns the entries (d, column) with d = tid / 32 + 8 e.  The chunks' sums do not depend
+    // on the state, so they are asked for four chunks ahead: a chunk then costs an addition, not a
+    // round trip to L2.
+    constexpr int AHEAD = 4;
+    auto weight_of = [&](int c) {
+        const int n = min(32, count - c * 32);
+        if (gated) return pp.gate_arrays[((first + c * 32 + n - 1) * heads + head) * 5 + 3];
+        float carried = 1.0f;
+        for (int i = 0; i < n; i++) carried *= p.decay[head];
+        return carried;
+    };
     for (int d0 = tid >> 5; d0 < dim; d0 += 8 * 8) {
-        float S[8], delta[8];
+        float S[8], ring[AHEAD][8], weights[AHEAD];
+        auto ask = [&](int c, int place) {
+            const float* slot = pp.chunk_state + ((long)(chunk + c) * heads + head) * dim * vdim;
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                const int d = d0 + 8 * e;
+                ring[place][e] = (active && d < dim) ? slot[(long)d * vdim + column] : 0.0f;
+            }
+            weights[place] = weight_of(c);
+        };
 #pragma unroll
         for (int e = 0; e < 8; e++) {
             const int d = d0 + 8 * e;
             S[e] = (active && d < dim) ? S_held[(long)d * vdim + column] : 0.0f;
         }
-        for (int c = 0; c < n_chunks; c++) {
-            const int n = min(32, count - c * 32);
-            float carried;
-            if (gated) carried = pp.gate_arrays[((first + c * 32 + n - 1) * heads + head) * 5 + 3];
-            else {
-                carried = 1.0f;
-                for (int i = 0; i < n; i++) carried *= p.decay[head];
-            }
-            float* slot = pp.chunk_state + ((long)(chunk + c) * heads + head) * dim * vdim;
 #pragma unroll
-            for (int e = 0; e < 8; e++) {
-                const int d = d0 + 8 * e;
-                delta[e] = (active && d < dim) ? slot[(long)d * vdim + column] : 0.0f;
-            }
+        for (int a = 0; a < AHEAD; a++)
+            if (a < n_chunks) ask(a, a);
+        for (int c0 = 0; c0 < n_chunks; c0 += AHEAD) {
 #pragma unroll
-            for (int e = 0; e < 8; e++) {
-                const int d = d0 + 8 * e;
-                if (active && d < dim) slot[(long)d * vdim + column] = S[e];
-                S[e] = fmaf(carried, S[e], delta[e]);
+            for (int a = 0; a < AHEAD; a++) {
+                const int c = c0 + a;
+                if (c < n_chunks) {
+                    float delta[8];
+#pragma unroll
+                    for (int e = 0; e < 8; e++) delta[e] = ring[a][e];
+                    const float carried = weights[a];
+                    if (c + AHEAD < n_chunks) ask(c + AHEAD, a);
+                    float* slot = pp.chunk_state + ((long)(chunk + c) * heads + head) * dim * vdim;
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        const int d = d0 + 8 * e;
+                        if (active && d < dim) slot[(long)d * vdim + column] = S[e];
+                        S[e] = fmaf(carried, S[e], delta[e]);
+                    }
+                }
             }
         }
         if (p.writes) {
