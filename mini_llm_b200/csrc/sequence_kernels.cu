@@ -11,7 +11,9 @@
 // path; bfloat16: the serving path).  Norm statistics, angles, scores, softmax, gates, decays
 // and all recurrent state are 32-bit in both.  A step's entries are read from device arrays
 // (slot, first row, rows, first position per entry), so a step of one shape launches the same
-// kernels with the same arguments.
+// kernels with the same arguments.  Every kernel is launched as a programmatic dependent of the
+// kernel before it on its stream: its blocks may be scheduled while that one still runs, and the
+// first thing each does is to wait for it, before any memory is touched.
 #include "common.cuh"
 
 MLLM_DEFINE_ERROR_API(mllm_sequence)
@@ -34,6 +36,8 @@ template <typename O, typename G, bool ADD, bool GATE>
 __global__ void grouped_rms_norm_kernel(O* __restrict__ out, long ld_out, const float* x, long ld_x,
                                         const float* __restrict__ gain, const int* __restrict__ rows,
                                         const G* __restrict__ gate, long ld_gate, int size, float eps) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
     __shared__ float scratch[33];
     const int r = blockIdx.x, g = blockIdx.y;
     const float* part = x + (long)(rows ? rows[r] : r) * ld_x + (long)g * size;
@@ -58,9 +62,9 @@ static void launch_grouped_rms_norm(void* out, long ld_out, const float* x, long
     dim3 grid(n_rows, groups);
     O* o = (O*)out;
     const G* g = (const G*)gate;
-    if (add) grouped_rms_norm_kernel<O, G, true, false><<<grid, threads, 0, s>>>(o, ld_out, x, ld_x, gain, rows, g, ld_gate, size, eps);
-    else if (gate != nullptr) grouped_rms_norm_kernel<O, G, false, true><<<grid, threads, 0, s>>>(o, ld_out, x, ld_x, gain, rows, g, ld_gate, size, eps);
-    else grouped_rms_norm_kernel<O, G, false, false><<<grid, threads, 0, s>>>(o, ld_out, x, ld_x, gain, rows, g, ld_gate, size, eps);
+    if (add) launch_kernel(g_dependent_launch != 0, grouped_rms_norm_kernel<O, G, true, false>, dim3(grid), dim3(threads), 0, s, o, ld_out, x, ld_x, gain, rows, g, ld_gate, size, eps);
+    else if (gate != nullptr) launch_kernel(g_dependent_launch != 0, grouped_rms_norm_kernel<O, G, false, true>, dim3(grid), dim3(threads), 0, s, o, ld_out, x, ld_x, gain, rows, g, ld_gate, size, eps);
+    else launch_kernel(g_dependent_launch != 0, grouped_rms_norm_kernel<O, G, false, false>, dim3(grid), dim3(threads), 0, s, o, ld_out, x, ld_x, gain, rows, g, ld_gate, size, eps);
 }
 
 // out_dtype / gate_dtype: element types of out and gate.  add != 0: out is fp32 and is added to.
@@ -96,6 +100,8 @@ __global__ void causal_taps_kernel(T* __restrict__ out, const T* __restrict__ h,
                                    const float* __restrict__ state, long state_stride, const int* __restrict__ positions,
                                    const int* __restrict__ token_item, const int* __restrict__ item_slot,
                                    const int* __restrict__ item_start, int width, int taps) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
     const int t = blockIdx.x;
     const int item = token_item[t];
     const int local = positions[t] - item_start[item];          // tokens of this request before t in this step
@@ -118,6 +124,8 @@ template <typename T>
 __global__ void causal_taps_state_kernel(float* __restrict__ state, long state_stride, const T* __restrict__ h,
                                          const int* __restrict__ item_slot, const int* __restrict__ item_offset,
                                          const int* __restrict__ item_count, int width, int taps) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
     const int item = blockIdx.x;
     const int count = item_count[item];
     if (count <= 0) return;
@@ -133,6 +141,62 @@ __global__ void causal_taps_state_kernel(float* __restrict__ state, long state_s
     }
 }
 
+// A step of single tokens: the norm in groups, the filter and the move of its state as one kernel.
+// Every entry brings one token, so all earlier inputs come from the state, and the block that
+// reads an entry's state is the only one that writes it.  x: the 32-bit stream; the normed value
+// is rounded to the activations' type before it is filtered and kept, as the separate kernels do.
+template <typename T>
+__global__ void norm_taps_step_kernel(T* __restrict__ out, const float* __restrict__ x, const float* __restrict__ gain,
+                                      const float* __restrict__ w, float* __restrict__ state, long state_stride,
+                                      const int* __restrict__ token_item, const int* __restrict__ item_slot, int width,
+                                      int groups, float eps, int taps, int writes) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
+    extern __shared__ float scale_of_group[];
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    const int size = width / groups;
+    const float* row = x + (long)t * width;
+    for (int g = warp; g < groups; g += n_warps) {
+        float sq = 0.0f;
+        for (int d = lane; d < size; d += 32) sq = fmaf(row[g * size + d], row[g * size + d], sq);
+        sq = warp_sum(sq);
+        if (lane == 0) scale_of_group[g] = 1.0f / sqrtf(sq / (float)size + eps);
+    }
+    __syncthreads();
+    float* held = state + (long)item_slot[token_item[t]] * state_stride;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float mine = to_f32(from_f32<T>(row[c] * scale_of_group[c / size] * gain[c]));
+        float acc = mine;
+        for (int s = 0; s < taps - 1; s++) acc = fmaf(w[(long)c * taps + s], held[(long)s * width + c], acc);
+        acc = fmaf(w[(long)c * taps + taps - 1], mine, acc);
+        out[(long)t * width + c] = from_f32<T>(acc);
+        if (writes) {
+            for (int s = 0; s + 1 < taps - 1; s++) held[(long)s * width + c] = held[(long)(s + 1) * width + c];
+            if (taps > 1) held[(long)(taps - 2) * width + c] = mine;
+        }
+    }
+}
+
+extern "C" int mllm_sequence_norm_taps_step(void* out, const float* x, const float* gain, const float* w, float* state,
+                                            long state_stride, const int* token_item, const int* item_slot, int n_tokens,
+                                            int width, int groups, float eps, int taps, int writes, int dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (taps < 1 || groups <= 0 || width % groups != 0) return fail("norm_taps_step: bad sizes");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = width >= 256 ? 256 : 64;
+    const size_t shared = (size_t)groups * sizeof(float);
+    if (shared > 48 * 1024) return fail("norm_taps_step: too many groups");
+    if (dtype == DT_F32)
+        launch_kernel(g_dependent_launch != 0, norm_taps_step_kernel<float>, dim3(n_tokens), dim3(threads), shared, s, (float*)out, x,
+                      gain, w, state, state_stride, token_item, item_slot, width, groups, eps, taps, writes);
+    else if (dtype == DT_BF16)
+        launch_kernel(g_dependent_launch != 0, norm_taps_step_kernel<bf16>, dim3(n_tokens), dim3(threads), shared, s, (bf16*)out, x,
+                      gain, w, state, state_stride, token_item, item_slot, width, groups, eps, taps, writes);
+    else
+        return fail("norm_taps_step: unknown dtype");
+    return check_launch("norm_taps_step_kernel");
+}
+
 extern "C" int mllm_sequence_causal_taps(void* out, const void* h, const float* w, float* state, long state_stride,
                                          const int* positions, const int* token_item, const int* item_slot,
                                          const int* item_start, const int* item_offset, const int* item_count,
@@ -142,16 +206,16 @@ extern "C" int mllm_sequence_causal_taps(void* out, const void* h, const float* 
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = width >= 256 ? 256 : 64;
     if (dtype == DT_F32) {
-        causal_taps_kernel<float><<<n_tokens, threads, 0, s>>>((float*)out, (const float*)h, w, state, state_stride, positions,
+        launch_kernel(g_dependent_launch != 0, causal_taps_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (float*)out, (const float*)h, w, state, state_stride, positions,
                                                                token_item, item_slot, item_start, width, taps);
         if (writes && taps > 1)
-            causal_taps_state_kernel<float><<<n_items, threads, 0, s>>>(state, state_stride, (const float*)h, item_slot,
+            launch_kernel(g_dependent_launch != 0, causal_taps_state_kernel<float>, dim3(n_items), dim3(threads), 0, s, state, state_stride, (const float*)h, item_slot,
                                                                         item_offset, item_count, width, taps);
     } else if (dtype == DT_BF16) {
-        causal_taps_kernel<bf16><<<n_tokens, threads, 0, s>>>((bf16*)out, (const bf16*)h, w, state, state_stride, positions,
+        launch_kernel(g_dependent_launch != 0, causal_taps_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, (bf16*)out, (const bf16*)h, w, state, state_stride, positions,
                                                               token_item, item_slot, item_start, width, taps);
         if (writes && taps > 1)
-            causal_taps_state_kernel<bf16><<<n_items, threads, 0, s>>>(state, state_stride, (const bf16*)h, item_slot,
+            launch_kernel(g_dependent_launch != 0, causal_taps_state_kernel<bf16>, dim3(n_items), dim3(threads), 0, s, state, state_stride, (const bf16*)h, item_slot,
                                                                        item_offset, item_count, width, taps);
     } else {
         return fail("causal_taps: unknown dtype");
@@ -178,6 +242,8 @@ __global__ void latent_prepare_kernel(T* __restrict__ pages, float* __restrict__
                                       const int* __restrict__ token_item, const int* __restrict__ block_table,
                                       int max_blocks, int page_size, int rank, int rot, int rot_dims, int heads, int dim,
                                       float eps, int writes) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
     __shared__ float scratch[33];
     extern __shared__ float turn[];                  // cos[rot_dims / 2], sin[rot_dims / 2]
     const int t = blockIdx.x;
@@ -228,11 +294,11 @@ extern "C" int mllm_sequence_latent_prepare(void* pages, float* q_eff, const flo
     cudaStream_t s = (cudaStream_t)stream;
     const size_t shared = (size_t)(rot_dims > 0 ? rot_dims : 1) * sizeof(float);
     if (dtype == DT_F32)
-        latent_prepare_kernel<float><<<n_tokens, 128, shared, s>>>((float*)pages, q_eff, down, (const float*)q, ld_q, gain, inv_freq,
+        launch_kernel(g_dependent_launch != 0, latent_prepare_kernel<float>, dim3(n_tokens), dim3(128), shared, s, (float*)pages, q_eff, down, (const float*)q, ld_q, gain, inv_freq,
                                                                    positions, token_item, block_table, max_blocks, page_size,
                                                                    rank, rot, rot_dims, heads, dim, eps, writes);
     else if (dtype == DT_BF16)
-        latent_prepare_kernel<bf16><<<n_tokens, 128, shared, s>>>((bf16*)pages, q_eff, down, (const bf16*)q, ld_q, gain, inv_freq,
+        launch_kernel(g_dependent_launch != 0, latent_prepare_kernel<bf16>, dim3(n_tokens), dim3(128), shared, s, (bf16*)pages, q_eff, down, (const bf16*)q, ld_q, gain, inv_freq,
                                                                   positions, token_item, block_table, max_blocks, page_size,
                                                                   rank, rot, rot_dims, heads, dim, eps, writes);
     else
@@ -249,6 +315,8 @@ template <typename AT, typename WT, typename OT>
 __global__ void __launch_bounds__(256)
 head_linear_kernel(OT* __restrict__ out, const AT* __restrict__ a, const WT* __restrict__ w, int M, int N, int K, long lda,
                    long ldo, long a_head, long o_head) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
     constexpr int BM = 64, BN = 64, BK = 16;
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
@@ -304,6 +372,8 @@ template <typename AT, typename WT, typename OT>
 __global__ void __launch_bounds__(256)
 head_linear_few_rows_kernel(OT* __restrict__ out, const AT* __restrict__ a, const WT* __restrict__ w, int M, int N, int K,
                             long lda, long ldo, long a_head, long o_head) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
     extern __shared__ float rows[];                 // [M][K]
     const int head = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     a += (long)head * a_head;
@@ -341,10 +411,10 @@ extern "C" int mllm_sequence_head_linear(void* out, const void* a, const void* w
     dim3 few_grid((N + 7) / 8, heads);
 #define MLLM_HEAD_LINEAR(AT, WT, OT)                                                                                  \
     if (few)                                                                                                          \
-        head_linear_few_rows_kernel<AT, WT, OT><<<few_grid, 256, (size_t)M * K * sizeof(float), s>>>(                 \
+        launch_kernel(g_dependent_launch != 0, head_linear_few_rows_kernel<AT, WT, OT>, dim3(few_grid), dim3(256), (size_t)M * K * sizeof(float), s,                  \
             (OT*)out, (const AT*)a, (const WT*)w, M, N, K, lda, ldo, a_head, o_head);                                 \
     else                                                                                                              \
-        head_linear_kernel<AT, WT, OT><<<grid, 256, 0, s>>>((OT*)out, (const AT*)a, (const WT*)w, M, N, K, lda, ldo,  \
+        launch_kernel(g_dependent_launch != 0, head_linear_kernel<AT, WT, OT>, dim3(grid), dim3(256), 0, s, (OT*)out, (const AT*)a, (const WT*)w, M, N, K, lda, ldo,  \
                                                             a_head, o_head)
     if (a_dtype == DT_F32 && w_dtype == DT_F32 && out_dtype == DT_F32) { MLLM_HEAD_LINEAR(float, float, float); }
     else if (a_dtype == DT_BF16 && w_dtype == DT_BF16 && out_dtype == DT_F32) { MLLM_HEAD_LINEAR(bf16, bf16, float); }
@@ -368,6 +438,8 @@ __global__ void __launch_bounds__(128)
 latent_attention_kernel(float* __restrict__ out, const float* __restrict__ q_eff, const T* __restrict__ pages,
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ positions,
                         const int* __restrict__ token_item, int heads, int rank, int rot, int page_size, float scale) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
     const int t = blockIdx.x, h = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int p = positions[t];
@@ -432,13 +504,13 @@ static int launch_latent_attention(float* out, const float* q_eff, const void* p
     const T* pg = (const T*)pages;
     const int pieces = (rank + rot + 31) / 32;
     if (pieces <= 4)
-        latent_attention_kernel<T, 4><<<grid, 128, 0, s>>>(out, q_eff, pg, block_table, max_blocks, positions, token_item, heads, rank, rot, page_size, scale);
+        launch_kernel(g_dependent_launch != 0, latent_attention_kernel<T, 4>, dim3(grid), dim3(128), 0, s, out, q_eff, pg, block_table, max_blocks, positions, token_item, heads, rank, rot, page_size, scale);
     else if (pieces <= 8)
-        latent_attention_kernel<T, 8><<<grid, 128, 0, s>>>(out, q_eff, pg, block_table, max_blocks, positions, token_item, heads, rank, rot, page_size, scale);
+        launch_kernel(g_dependent_launch != 0, latent_attention_kernel<T, 8>, dim3(grid), dim3(128), 0, s, out, q_eff, pg, block_table, max_blocks, positions, token_item, heads, rank, rot, page_size, scale);
     else if (pieces <= 20)
-        latent_attention_kernel<T, 20><<<grid, 128, 0, s>>>(out, q_eff, pg, block_table, max_blocks, positions, token_item, heads, rank, rot, page_size, scale);
+        launch_kernel(g_dependent_launch != 0, latent_attention_kernel<T, 20>, dim3(grid), dim3(128), 0, s, out, q_eff, pg, block_table, max_blocks, positions, token_item, heads, rank, rot, page_size, scale);
     else if (pieces <= 36)
-        latent_attention_kernel<T, 36><<<grid, 128, 0, s>>>(out, q_eff, pg, block_table, max_blocks, positions, token_item, heads, rank, rot, page_size, scale);
+        launch_kernel(g_dependent_launch != 0, latent_attention_kernel<T, 36>, dim3(grid), dim3(128), 0, s, out, q_eff, pg, block_table, max_blocks, positions, token_item, heads, rank, rot, page_size, scale);
     else
         return fail("latent_attention: a cached row may hold at most 1152 entries");
     return check_launch("latent_attention_kernel");
@@ -509,6 +581,8 @@ __device__ __forceinline__ void unpack4(const uint2& c, float* v) {
 template <typename T, int RPT, int CT>
 __global__ void __launch_bounds__(256)
 latent_attention_tiled_kernel(LatentTiledParams p) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
     typedef typename Chunk4<T>::type chunk_t;
     constexpr int R = 32, BK = 32, CG = 8 * RPT;
     extern __shared__ __align__(16) unsigned char raw[];
@@ -713,6 +787,8 @@ latent_attention_tiled_kernel(LatentTiledParams p) {
 // The parts of a (token, head) into one result, in the order of the parts.
 __global__ void latent_merge_kernel(void* __restrict__ out, int out_bf16, const float* __restrict__ part_out,
                                     const float* __restrict__ part_ml, int parts, int rank) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
     const long at = blockIdx.x;
     const float* ml = part_ml + at * parts * 2;
     float big = -INFINITY;
@@ -738,7 +814,7 @@ template <typename T, int RPT, int CT>
 static int launch_latent_tiled(const LatentTiledParams& p, dim3 grid, size_t shared, cudaStream_t s) {
     if (shared > 48 * 1024)
         cudaFuncSetAttribute(latent_attention_tiled_kernel<T, RPT, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-    latent_attention_tiled_kernel<T, RPT, CT><<<grid, 256, shared, s>>>(p);
+    launch_kernel(g_dependent_launch != 0, latent_attention_tiled_kernel<T, RPT, CT>, dim3(grid), dim3(256), shared, s, p);
     return check_launch("latent_attention_tiled_kernel");
 }
 
@@ -771,7 +847,7 @@ extern "C" int mllm_sequence_latent_attention_tiled(const LatentTiledParams* par
     else if (dtype == DT_BF16) rc = pick_latent_tiled<bf16>(p, grid, shared, s);
     else return fail("latent_attention_tiled: unknown dtype");
     if (rc != 0 || p.parts == 1) return rc;
-    latent_merge_kernel<<<(unsigned)((long)n_units * p.heads), 128, 0, s>>>(p.out, p.out_bf16, p.part_out, p.part_ml, p.parts, p.rank);
+    launch_kernel(g_dependent_launch != 0, latent_merge_kernel, dim3((unsigned)((long)n_units * p.heads)), dim3(128), 0, s, p.out, p.out_bf16, p.part_out, p.part_ml, p.parts, p.rank);
     return check_launch("latent_merge_kernel");
 }
 
@@ -807,6 +883,8 @@ struct MemoryScanParams {
 template <typename T, int VS>
 __global__ void __launch_bounds__(VS)
 memory_scan_kernel(MemoryScanParams p) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
     extern __shared__ float shared[];
     const int item = blockIdx.x, head = blockIdx.y, v0 = blockIdx.z * VS, tid = threadIdx.x;
     const int count = p.item_count[item];
@@ -907,10 +985,10 @@ extern "C" int mllm_sequence_memory_scan(const MemoryScanParams* params, int n_i
     dim3 grid(n_items, p.heads, (p.vdim + VS - 1) / VS);
     if (dtype == DT_F32) {
         if (shared > 48 * 1024) cudaFuncSetAttribute(memory_scan_kernel<float, VS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-        memory_scan_kernel<float, VS><<<grid, VS, shared, s>>>(p);
+        launch_kernel(g_dependent_launch != 0, memory_scan_kernel<float, VS>, dim3(grid), dim3(VS), shared, s, p);
     } else if (dtype == DT_BF16) {
         if (shared > 48 * 1024) cudaFuncSetAttribute(memory_scan_kernel<bf16, VS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-        memory_scan_kernel<bf16, VS><<<grid, VS, shared, s>>>(p);
+        launch_kernel(g_dependent_launch != 0, memory_scan_kernel<bf16, VS>, dim3(grid), dim3(VS), shared, s, p);
     } else {
         return fail("memory_scan: unknown dtype");
     }
@@ -934,6 +1012,8 @@ extern "C" int mllm_sequence_memory_scan(const MemoryScanParams* params, int n_i
 template <typename T>
 __global__ void __launch_bounds__(256)
 memory_chunk_kernel(MemoryScanParams p) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
     constexpr int C = 32, VS = 32;
     extern __shared__ __align__(16) float shared[];
     const int item = blockIdx.x, head = blockIdx.y, v0 = blockIdx.z * VS, tid = threadIdx.x;
@@ -1225,10 +1305,10 @@ extern "C" int mllm_sequence_memory_chunk(const MemoryScanParams* params, int n_
     dim3 grid(n_items, p.heads, (p.vdim + 31) / 32);
     if (dtype == DT_F32) {
         if (shared > 48 * 1024) cudaFuncSetAttribute(memory_chunk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-        memory_chunk_kernel<float><<<grid, 256, shared, s>>>(p);
+        launch_kernel(g_dependent_launch != 0, memory_chunk_kernel<float>, dim3(grid), dim3(256), shared, s, p);
     } else if (dtype == DT_BF16) {
         if (shared > 48 * 1024) cudaFuncSetAttribute(memory_chunk_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-        memory_chunk_kernel<bf16><<<grid, 256, shared, s>>>(p);
+        launch_kernel(g_dependent_launch != 0, memory_chunk_kernel<bf16>, dim3(grid), dim3(256), shared, s, p);
     } else {
         return fail("memory_chunk: unknown dtype");
     }
@@ -1272,6 +1352,8 @@ __device__ __forceinline__ bool find_chunk(const int* __restrict__ item_count, i
 }
 
 __global__ void __launch_bounds__(32) memory_gates_kernel(MemoryPassParams pp) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
     const MemoryScanParams& p = pp.base;
     const int item = blockIdx.x, head = blockIdx.y, lane = threadIdx.x, heads = p.heads;
     const int count = p.item_count[item];
@@ -1361,6 +1443,8 @@ __device__ __forceinline__ void load_chunk_rows(const MemoryScanParams& p, const
 
 template <typename T>
 __global__ void __launch_bounds__(256) memory_sums_kernel(MemoryPassParams pp) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
     const MemoryScanParams& p = pp.base;
     ChunkPlace at;
     if (!place_chunk(pp, at)) return;
@@ -1409,6 +1493,8 @@ __global__ void __launch_bounds__(256) memory_sums_kernel(MemoryPassParams pp) {
 }
 
 __global__ void __launch_bounds__(256) memory_carry_kernel(MemoryPassParams pp) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
     const MemoryScanParams& p = pp.base;
     const int item = blockIdx.x, head = blockIdx.y, v0 = blockIdx.z * 32, tid = threadIdx.x;
     const int heads = p.heads, dim = p.dim, vdim = p.vdim;
@@ -1500,6 +1586,8 @@ __global__ void __launch_bounds__(256) memory_carry_kernel(MemoryPassParams pp) 
 
 template <typename T>
 __global__ void __launch_bounds__(256) memory_read_kernel(MemoryPassParams pp) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
     const MemoryScanParams& p = pp.base;
     ChunkPlace at;
     if (!place_chunk(pp, at)) return;
@@ -1628,24 +1716,24 @@ extern "C" int mllm_sequence_memory_passes(const MemoryPassParams* params, int d
     cudaStream_t s = (cudaStream_t)stream;
     const bool gated = p.gates != nullptr;
     const int slices = (p.vdim + 31) / 32;
-    if (gated) memory_gates_kernel<<<dim3(pp.n_items, p.heads), 32, 0, s>>>(pp);
+    if (gated) launch_kernel(g_dependent_launch != 0, memory_gates_kernel, dim3(dim3(pp.n_items, p.heads)), dim3(32), 0, s, pp);
     dim3 over_chunks(pp.max_chunks, p.heads, slices), over_items(pp.n_items, p.heads, slices);
     if (dtype == DT_F32) {
         if (shared > 48 * 1024) {
             cudaFuncSetAttribute(memory_sums_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
             cudaFuncSetAttribute(memory_read_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
         }
-        memory_sums_kernel<float><<<over_chunks, 256, shared, s>>>(pp);
-        memory_carry_kernel<<<over_items, 256, 0, s>>>(pp);
-        memory_read_kernel<float><<<over_chunks, 256, shared, s>>>(pp);
+        launch_kernel(g_dependent_launch != 0, memory_sums_kernel<float>, dim3(over_chunks), dim3(256), shared, s, pp);
+        launch_kernel(g_dependent_launch != 0, memory_carry_kernel, dim3(over_items), dim3(256), 0, s, pp);
+        launch_kernel(g_dependent_launch != 0, memory_read_kernel<float>, dim3(over_chunks), dim3(256), shared, s, pp);
     } else if (dtype == DT_BF16) {
         if (shared > 48 * 1024) {
             cudaFuncSetAttribute(memory_sums_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
             cudaFuncSetAttribute(memory_read_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
         }
-        memory_sums_kernel<bf16><<<over_chunks, 256, shared, s>>>(pp);
-        memory_carry_kernel<<<over_items, 256, 0, s>>>(pp);
-        memory_read_kernel<bf16><<<over_chunks, 256, shared, s>>>(pp);
+        launch_kernel(g_dependent_launch != 0, memory_sums_kernel<bf16>, dim3(over_chunks), dim3(256), shared, s, pp);
+        launch_kernel(g_dependent_launch != 0, memory_carry_kernel, dim3(over_items), dim3(256), 0, s, pp);
+        launch_kernel(g_dependent_launch != 0, memory_read_kernel<bf16>, dim3(over_chunks), dim3(256), shared, s, pp);
     } else {
         return fail("memory_passes: unknown dtype");
     }
@@ -1659,6 +1747,8 @@ extern "C" int mllm_sequence_memory_passes(const MemoryPassParams* params, int d
 // ---------------------------------------------------------------------------
 __global__ void depth_mix_kernel(float* __restrict__ hidden, float* __restrict__ kept, const float* __restrict__ w, int index,
                                  int planes, int width, long n) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
     const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const long t = i / width;
@@ -1677,6 +1767,6 @@ extern "C" int mllm_sequence_depth_mix(float* hidden, float* kept, const float* 
     if (n_tokens <= 0) return 0;
     if (index < 0 || index >= planes) return fail("depth_mix: the result's index is outside the kept planes");
     const long n = (long)n_tokens * width;
-    depth_mix_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(hidden, kept, w, index, planes, width, n);
+    launch_kernel(g_dependent_launch != 0, depth_mix_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, hidden, kept, w, index, planes, width, n);
     return check_launch("depth_mix_kernel");
 }

@@ -97,6 +97,14 @@ class Kernels:
         return ops.grouped_rms_norm(out, x, gain, groups, eps, rows, gate, add)
 
     def causal_taps(self, ctx, out, h, w, state, writes=True):
+        if isinstance(h, DeferredNorm):
+            if h.kind == "grouped_rms_norm" and h.rows is None and ctx.decode_only and w.shape[1] > 1:
+                # single tokens: norm, filter and the state's move in one kernel
+                self.launches += 1
+                self.chose("causal_taps", "norm_taps_step", out.shape[0], out.shape[1], w.shape[1])
+                return ops.norm_taps_step(out, h.x, h.gain, h.groups, h.eps, w, state, ctx.token_item, ctx.item_slot, writes)
+            h = h.materialize(ctx)
+        self.chose("causal_taps", "causal_taps", out.shape[0], out.shape[1], w.shape[1])
         self.launches += 2 if writes and w.shape[1] > 1 else 1
         return ops.causal_taps(out, h, w, state, ctx.positions, ctx.token_item, ctx.item_slot, ctx.item_start,
                                ctx.item_offset, ctx.item_count, writes)

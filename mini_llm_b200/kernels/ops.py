@@ -843,6 +843,30 @@ def causal_taps(out, h, w, state, positions, token_item, item_slot, item_start, 
     return out
 
 
+_norm_taps_step = Function("sequence", "mllm_sequence_norm_taps_step", [P, P, P, P, P, L, P, P, I, I, I, F, I, I, I, P])
+
+
+def norm_taps_step(out, x, gain, groups, eps, w, state, token_item, item_slot, writes=True):
+    """A step of single tokens (one per entry): ``grouped_rms_norm`` of the fp32 rows ``x``, then
+    ``causal_taps`` with every earlier input from ``state``, then the state moved on, in one kernel."""
+    _check(out, "norm_taps_step.out", None, 2)
+    _check(x, "norm_taps_step.x", torch.float32, 2)
+    _check(gain, "norm_taps_step.gain", torch.float32, 1)
+    _check(w, "norm_taps_step.w", torch.float32, 2)
+    _check(state, "norm_taps_step.state", torch.float32, 3)
+    n, width = out.shape
+    taps = w.shape[1]
+    if (not (out.is_contiguous() and x.is_contiguous() and w.is_contiguous()) or x.shape[0] < n or x.shape[1] != width
+            or gain.shape[0] != width or w.shape[0] != width or width % groups != 0):
+        raise KernelError("norm_taps_step: sizes do not agree")
+    if taps < 2 or tuple(state.shape[1:]) != (taps - 1, width) or state.stride(1) != width:
+        raise KernelError(f"norm_taps_step: the state must be [slots, {taps - 1}, {width}]")
+    _norm_taps_step(out.data_ptr(), x.data_ptr(), gain.data_ptr(), w.data_ptr(), state.data_ptr(), state.stride(0),
+                    token_item.data_ptr(), item_slot.data_ptr(), n, width, int(groups), float(eps), taps, int(bool(writes)),
+                    dtype_code(out.dtype), _stream())
+    return out
+
+
 _latent_prepare = Function("sequence", "mllm_sequence_latent_prepare",
                            [P, P, P, P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P])
 

@@ -44,9 +44,11 @@ class SandwichNorm(Arrangement):
 
     def run(self, ctx, parts, hidden, cache):
         composite = getattr(cache, "kind", "none") == "composite"
-        x = parts["norm_1"].forward(ctx, hidden, tag="norm_1")
         if "input_filter" in parts:
+            x = parts["norm_1"].forward(ctx, hidden, tag="norm_1", **_defer(parts["norm_1"], parts["input_filter"]))
             x = parts["input_filter"].forward(ctx, x, cache.of("input_filter") if composite else cache)
+        else:
+            x = parts["norm_1"].forward(ctx, hidden, tag="norm_1")
         y = parts["mixer"].compute(ctx, x, cache.of("mixer") if composite else cache)
         parts["norm_1b"].add_normed(ctx, hidden, y)
         if "feed_forward" in parts:

@@ -16,6 +16,7 @@ from .spec import FixedState, NoCache, WeightSpec
 
 class CausalTaps(InputFilter):
     graph_safe = True
+    accepts_deferred_norm = True      # a step of single tokens norms on the way in (one kernel with the filter)
 
     def __init__(self, prefix, width: int, taps: int, name: str = "weight"):
         super().__init__(prefix)
@@ -40,7 +41,7 @@ class CausalTaps(InputFilter):
             state, writes = cache.state, cache.writes
         else:
             if self._no_state is None:
-                self._no_state = torch.zeros((1, 0, self.width), dtype=torch.float32, device=x.device)
+                self._no_state = torch.zeros((1, 0, self.width), dtype=torch.float32, device=ctx.device)
             state, writes = self._no_state, False
         ctx.kernels.causal_taps(ctx, out, x, self.w(self.name), state, writes)
         return out

@@ -44,6 +44,7 @@ class LayerNorm(Norm):
 
 class GroupedRmsNorm(Norm):
     graph_safe = True
+    can_defer = True
 
     def __init__(self, prefix, width: int, eps: float, groups: int = 1, name: str = "weight"):
         super().__init__(prefix)
@@ -54,7 +55,12 @@ class GroupedRmsNorm(Norm):
     def weight_specs(self):
         return [WeightSpec(self.full_name(self.name), (self.width,), role="vector", init="gain")]
 
-    def forward(self, ctx, x, rows=None, tag="norm"):
+    def forward(self, ctx, x, rows=None, tag="norm", defer=False):
+        if defer:
+            gain = self.w(self.name)
+            return DeferredNorm("grouped_rms_norm", x, rows, tag,
+                                lambda c, out: c.kernels.grouped_rms_norm(out, x, gain, self.groups, self.eps, rows),
+                                gain=gain, groups=self.groups, eps=self.eps)
         n_rows = x.shape[0] if rows is None else rows.shape[0]
         out = ctx.buffer(tag, (n_rows, self.width), ctx.act_dtype)
         ctx.kernels.grouped_rms_norm(out, x, self.w(self.name), self.groups, self.eps, rows)
