@@ -77,7 +77,7 @@ def test_plain_mixers_do_not_look_ahead():
     parsed = config_from_dict(raw)
     from mini_llm_b200.weights.random_init import random_tensors
     tensors = {k: v.astype(np.float64) for k, v in random_tensors(describe_model(parsed), 1, "varied").items()}
-    tokens = fx.random_tokens(1, 20, 211) if hasattr(fx, "random_tokens") else list(np.random.default_rng(1).integers(0, 211, 20))
+    tokens = [int(t) for t in np.random.default_rng(1).integers(0, 211, 20)]
     whole = plain.forward(raw, tensors, tokens)
     part = plain.forward(raw, tensors, tokens[:13])
     np.testing.assert_allclose(whole[:13], part, atol=1e-12)

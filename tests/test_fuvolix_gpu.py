@@ -28,7 +28,7 @@ def engine_for(folder, dtype="float32", **options):
 def check(engine, folder, requests, steps, atol=F32_ATOL):
     got = run_schedule(engine, requests, steps)
     for name, tokens in requests.items():
-        expected = plain_logits = fx.plain_logits(folder, tokens)
+        expected = fx.plain_logits(folder, tokens)
         worst = np.abs(got[name] - expected).max(axis=1)
         assert worst.max() <= atol, f"request {name}: first wrong token {int(np.argmax(worst > atol))} of {len(tokens)}, off by {worst.max():.2e}"
     engine.cache.check()
