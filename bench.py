@@ -819,7 +819,7 @@ def mixer_kernels(torch, size: dict, peak: dict):
                                                                          rank, rot, page, 0.1, tiles=tiles_d, n_tiles=len(tiles)))
             add(f"latent attention in tiles, {name}", us, flops=2.0 * pairs * (row + rank), heads=heads, row=row)
         else:
-            parts = max(1, min(32, 296 // (n * -(-heads // 32))))
+            parts = max(1, min(32, 296 // (n * (1 if heads <= 16 else -(-heads // 32)))))
             scratch = (torch.empty(n * heads * parts * rank, device="cuda"), torch.empty(n * heads * parts * 2, device="cuda"))
             us = replayed_us(torch, lambda i: ops.latent_attention_tiled(out, q_eff, pages[i % 4], table, positions, token_item, heads,
                                                                          rank, rot, page, 0.1, parts=parts, scratch=scratch))

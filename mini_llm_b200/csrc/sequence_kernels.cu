@@ -578,13 +578,15 @@ __device__ __forceinline__ void unpack4(const uint2& c, float* v) {
     v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
 }
 
-template <typename T, int RPT, int CT>
+template <typename T, int R, int RPT, int CT>
 __global__ void __launch_bounds__(256)
 latent_attention_tiled_kernel(LatentTiledParams p) {
     dependents_may_start();
     wait_for_earlier_kernels();
     typedef typename Chunk4<T>::type chunk_t;
-    constexpr int R = 32, BK = 32, CG = 8 * RPT;
+    // R rows a block: 32, or 16 for single tokens of models with up to 16 heads (no thread then
+    // computes for a row that is nobody's); RW rows per warp in the softmax, RP per thread in the scores
+    constexpr int BK = 32, CG = 256 / (R / RPT), RW = R / 8, RP = R / 16;
     extern __shared__ __align__(16) unsigned char raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int row_width = p.rank + p.rot, ld = row_width + 4;
@@ -634,9 +636,9 @@ latent_attention_tiled_kernel(LatentTiledParams p) {
         const int token = tid / p.HB;
         row_position[tid] = first_position + (token < rows ? token : 0);
     }
-    float m_row[4], l_row[4];                                       // of rows 4 * warp + i, the same in every lane
+    float m_row[RW], l_row[RW];                                     // of rows RW * warp + i, the same in every lane
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
+    for (int i = 0; i < RW; i++) {
         m_row[i] = -INFINITY;
         l_row[i] = 0.0f;
     }
@@ -678,28 +680,42 @@ latent_attention_tiled_kernel(LatentTiledParams p) {
         __syncthreads();                                            // (Qs and row_position are written, too)
         // scores: rows rp, rp + 16 against keys jp, jp + 16
         {
-            float s00 = 0.0f, s01 = 0.0f, s10 = 0.0f, s11 = 0.0f;
-            for (int d = 0; d < row_width; d += 4) {
-                const float4 qa = *reinterpret_cast<const float4*>(Qs + rp * ld + d);
-                const float4 qb = *reinterpret_cast<const float4*>(Qs + (rp + 16) * ld + d);
-                float ka[4], kb[4];
-                unpack4(*reinterpret_cast<const chunk_t*>(Ks + jp * ld + d), ka);
-                unpack4(*reinterpret_cast<const chunk_t*>(Ks + (jp + 16) * ld + d), kb);
-                s00 = fmaf(qa.x, ka[0], fmaf(qa.y, ka[1], fmaf(qa.z, ka[2], fmaf(qa.w, ka[3], s00))));
-                s01 = fmaf(qa.x, kb[0], fmaf(qa.y, kb[1], fmaf(qa.z, kb[2], fmaf(qa.w, kb[3], s01))));
-                s10 = fmaf(qb.x, ka[0], fmaf(qb.y, ka[1], fmaf(qb.z, ka[2], fmaf(qb.w, ka[3], s10))));
-                s11 = fmaf(qb.x, kb[0], fmaf(qb.y, kb[1], fmaf(qb.z, kb[2], fmaf(qb.w, kb[3], s11))));
+            if constexpr (RP == 2) {
+                float s00 = 0.0f, s01 = 0.0f, s10 = 0.0f, s11 = 0.0f;
+                for (int d = 0; d < row_width; d += 4) {
+                    const float4 qa = *reinterpret_cast<const float4*>(Qs + rp * ld + d);
+                    const float4 qb = *reinterpret_cast<const float4*>(Qs + (rp + 16) * ld + d);
+                    float ka[4], kb[4];
+                    unpack4(*reinterpret_cast<const chunk_t*>(Ks + jp * ld + d), ka);
+                    unpack4(*reinterpret_cast<const chunk_t*>(Ks + (jp + 16) * ld + d), kb);
+                    s00 = fmaf(qa.x, ka[0], fmaf(qa.y, ka[1], fmaf(qa.z, ka[2], fmaf(qa.w, ka[3], s00))));
+                    s01 = fmaf(qa.x, kb[0], fmaf(qa.y, kb[1], fmaf(qa.z, kb[2], fmaf(qa.w, kb[3], s01))));
+                    s10 = fmaf(qb.x, ka[0], fmaf(qb.y, ka[1], fmaf(qb.z, ka[2], fmaf(qb.w, ka[3], s10))));
+                    s11 = fmaf(qb.x, kb[0], fmaf(qb.y, kb[1], fmaf(qb.z, kb[2], fmaf(qb.w, kb[3], s11))));
+                }
+                Ss[rp * (BK + 1) + jp] = s00;
+                Ss[rp * (BK + 1) + jp + 16] = s01;
+                Ss[(rp + 16) * (BK + 1) + jp] = s10;
+                Ss[(rp + 16) * (BK + 1) + jp + 16] = s11;
+            } else {
+                float s0 = 0.0f, s1 = 0.0f;
+                for (int d = 0; d < row_width; d += 4) {
+                    const float4 qa = *reinterpret_cast<const float4*>(Qs + rp * ld + d);
+                    float ka[4], kb[4];
+                    unpack4(*reinterpret_cast<const chunk_t*>(Ks + jp * ld + d), ka);
+                    unpack4(*reinterpret_cast<const chunk_t*>(Ks + (jp + 16) * ld + d), kb);
+                    s0 = fmaf(qa.x, ka[0], fmaf(qa.y, ka[1], fmaf(qa.z, ka[2], fmaf(qa.w, ka[3], s0))));
+                    s1 = fmaf(qa.x, kb[0], fmaf(qa.y, kb[1], fmaf(qa.z, kb[2], fmaf(qa.w, kb[3], s1))));
+                }
+                Ss[rp * (BK + 1) + jp] = s0;
+                Ss[rp * (BK + 1) + jp + 16] = s1;
             }
-            Ss[rp * (BK + 1) + jp] = s00;
-            Ss[rp * (BK + 1) + jp + 16] = s01;
-            Ss[(rp + 16) * (BK + 1) + jp] = s10;
-            Ss[(rp + 16) * (BK + 1) + jp + 16] = s11;
         }
         __syncthreads();
-        // softmax, online: warp w owns rows 4w .. 4w + 3, a lane a key
+        // softmax, online: warp w owns rows RW w .. RW w + RW - 1, a lane a key
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const int r = warp * 4 + i, key = k0 + lane;
+        for (int i = 0; i < RW; i++) {
+            const int r = warp * RW + i, key = k0 + lane;
             const bool seen = key < key_end && key <= row_position[r];
             const float sc = seen ? Ss[r * (BK + 1) + lane] * p.scale : -INFINITY;
             const float m_new = fmaxf(m_row[i], warp_max(sc));
@@ -744,9 +760,9 @@ latent_attention_tiled_kernel(LatentTiledParams p) {
     __syncthreads();
     if (lane == 0) {
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            sums[warp * 4 + i] = l_row[i];
-            factor[warp * 4 + i] = m_row[i];
+        for (int i = 0; i < RW; i++) {
+            sums[warp * RW + i] = l_row[i];
+            factor[warp * RW + i] = m_row[i];
         }
     }
     __syncthreads();
@@ -805,25 +821,32 @@ __global__ void latent_merge_kernel(void* __restrict__ out, int out_bf16, const 
     }
 }
 
-static size_t latent_tiled_shared_bytes(int row_width, int element_bytes, int key_buffers) {
+static size_t latent_tiled_shared_bytes(int rows, int row_width, int element_bytes, int key_buffers) {
     const size_t ld = (size_t)row_width + 4;
-    return 32 * ld * 4 + 32 * 33 * 4 + 64 * 4 + key_buffers * 32 * ld * (size_t)element_bytes;
+    return rows * ld * 4 + rows * 33 * 4 + 2 * rows * 4 + key_buffers * 32 * ld * (size_t)element_bytes;
 }
 
-template <typename T, int RPT, int CT>
+template <typename T, int R, int RPT, int CT>
 static int launch_latent_tiled(const LatentTiledParams& p, dim3 grid, size_t shared, cudaStream_t s) {
     if (shared > 48 * 1024)
-        cudaFuncSetAttribute(latent_attention_tiled_kernel<T, RPT, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-    launch_kernel(g_dependent_launch != 0, latent_attention_tiled_kernel<T, RPT, CT>, dim3(grid), dim3(256), shared, s, p);
+        cudaFuncSetAttribute(latent_attention_tiled_kernel<T, R, RPT, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    launch_kernel(g_dependent_launch != 0, latent_attention_tiled_kernel<T, R, RPT, CT>, dim3(grid), dim3(256), shared, s, p);
     return check_launch("latent_attention_tiled_kernel");
 }
 
+// (a thread's accumulators: RPT rows x 8 CT latent columns; 256 threads cover R rows x the latent)
 template <typename T>
-static int pick_latent_tiled(const LatentTiledParams& p, dim3 grid, size_t shared, cudaStream_t s) {
-    if (p.rank <= 128) return launch_latent_tiled<T, 2, 1>(p, grid, shared, s);
-    if (p.rank <= 256) return launch_latent_tiled<T, 4, 1>(p, grid, shared, s);
-    if (p.rank <= 512) return launch_latent_tiled<T, 8, 1>(p, grid, shared, s);
-    return launch_latent_tiled<T, 8, 2>(p, grid, shared, s);
+static int pick_latent_tiled(const LatentTiledParams& p, int rows, dim3 grid, size_t shared, cudaStream_t s) {
+    if (rows == 16) {
+        if (p.rank <= 128) return launch_latent_tiled<T, 16, 1, 1>(p, grid, shared, s);
+        if (p.rank <= 256) return launch_latent_tiled<T, 16, 2, 1>(p, grid, shared, s);
+        if (p.rank <= 512) return launch_latent_tiled<T, 16, 4, 1>(p, grid, shared, s);
+        return launch_latent_tiled<T, 16, 4, 2>(p, grid, shared, s);
+    }
+    if (p.rank <= 128) return launch_latent_tiled<T, 32, 2, 1>(p, grid, shared, s);
+    if (p.rank <= 256) return launch_latent_tiled<T, 32, 4, 1>(p, grid, shared, s);
+    if (p.rank <= 512) return launch_latent_tiled<T, 32, 8, 1>(p, grid, shared, s);
+    return launch_latent_tiled<T, 32, 8, 2>(p, grid, shared, s);
 }
 
 // n_units: records of `tiles` (prompt portions), or tokens (tiles null: single tokens, in `parts` parts).
@@ -832,19 +855,20 @@ extern "C" int mllm_sequence_latent_attention_tiled(const LatentTiledParams* par
     if (n_units <= 0) return 0;
     const int row_width = p.rank + p.rot;
     if (row_width % 4 != 0 || p.rank % 8 != 0 || p.rank > 1024) return fail("latent_attention_tiled: the row must be a multiple of 4 and the latent of 8, at most 1024");
-    if (p.HB <= 0 || p.TQ <= 0 || p.HB * p.TQ != 32 || 128 % p.TQ != 0) return fail("latent_attention_tiled: a block takes 32 rows");
+    const int rows = p.HB * p.TQ;
+    if (p.HB <= 0 || p.TQ <= 0 || (rows != 32 && rows != 16) || 128 % p.TQ != 0) return fail("latent_attention_tiled: a block takes 32 or 16 rows");
     if (p.tiles == nullptr && p.TQ != 1) return fail("latent_attention_tiled: single tokens come one per block");
     if (p.parts < 1 || (p.parts > 1 && (p.tiles != nullptr || p.part_out == nullptr || p.part_ml == nullptr)))
         return fail("latent_attention_tiled: parts are for single tokens and need scratch");
     const int element_bytes = dtype == DT_F32 ? 4 : 2;
-    p.key_buffers = latent_tiled_shared_bytes(row_width, element_bytes, 2) <= 220 * 1024 ? 2 : 1;
-    const size_t shared = latent_tiled_shared_bytes(row_width, element_bytes, p.key_buffers);
+    p.key_buffers = latent_tiled_shared_bytes(rows, row_width, element_bytes, 2) <= 220 * 1024 ? 2 : 1;
+    const size_t shared = latent_tiled_shared_bytes(rows, row_width, element_bytes, p.key_buffers);
     if (shared > 220 * 1024) return fail("latent_attention_tiled: the rows do not fit in shared memory");
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(p.tiles != nullptr ? n_units * (128 / p.TQ) : n_units, (p.heads + p.HB - 1) / p.HB, p.parts);
     int rc;
-    if (dtype == DT_F32) rc = pick_latent_tiled<float>(p, grid, shared, s);
-    else if (dtype == DT_BF16) rc = pick_latent_tiled<bf16>(p, grid, shared, s);
+    if (dtype == DT_F32) rc = pick_latent_tiled<float>(p, rows, grid, shared, s);
+    else if (dtype == DT_BF16) rc = pick_latent_tiled<bf16>(p, rows, grid, shared, s);
     else return fail("latent_attention_tiled: unknown dtype");
     if (rc != 0 || p.parts == 1) return rc;
     launch_kernel(g_dependent_launch != 0, latent_merge_kernel, dim3((unsigned)((long)n_units * p.heads)), dim3(128), 0, s, p.out, p.out_bf16, p.part_out, p.part_ml, p.parts, p.rank);

@@ -151,7 +151,7 @@ class Kernels:
             if ctx.decode_only:
                 # single tokens: all heads of a token share the cached rows; while the (token, head
                 # block) pairs are fewer than twice the SMs, each token's keys come in parts
-                blocks = n * -(-heads // ops.LATENT_TILE_ROWS)
+                blocks = n * (1 if heads <= 16 else -(-heads // ops.LATENT_TILE_ROWS))
                 parts = max(1, min(32, 296 // blocks))
                 scratch = self._latent_scratch(ctx.device, n * heads * parts * rank, n * heads * parts * 2) if parts > 1 else None
                 self.launches += 1 if parts > 1 else 0

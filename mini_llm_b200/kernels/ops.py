@@ -1001,7 +1001,8 @@ def latent_attention_tiled(out, q_eff, pages, block_table, positions, token_item
         params.TQ = LATENT_TILE_ROWS // params.HB
         params.parts, units = 1, n_tiles
     else:
-        params.HB, params.TQ, params.parts, units = LATENT_TILE_ROWS, 1, int(parts), n
+        # (a block of 16 rows where that holds every head: no thread then works for a row that is nobody's)
+        params.HB, params.TQ, params.parts, units = (16 if heads <= 16 else LATENT_TILE_ROWS), 1, int(parts), n
         if parts > 1:
             part_out, part_ml = scratch
             _check(part_out, "latent_attention.scratch", torch.float32)
