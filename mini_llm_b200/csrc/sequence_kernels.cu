@@ -805,19 +805,25 @@ __global__ void latent_merge_kernel(void* __restrict__ out, int out_bf16, const 
                                     const float* __restrict__ part_ml, int parts, int rank) {
     dependents_may_start();
     wait_for_earlier_kernels();
+    __shared__ float weight[32];                 // of each part (there are at most 32), already divided by the sum
     const long at = blockIdx.x;
-    const float* ml = part_ml + at * parts * 2;
-    float big = -INFINITY;
-    for (int z = 0; z < parts; z++) big = fmaxf(big, ml[2 * z]);
-    float total = 0.0f;
-    for (int z = 0; z < parts; z++)
-        if (ml[2 * z] != -INFINITY) total += ml[2 * z + 1] * expf(ml[2 * z] - big);
+    if (threadIdx.x < 32) {
+        const int z = threadIdx.x;
+        const float m = z < parts ? part_ml[(at * parts + z) * 2] : -INFINITY;
+        const float l = z < parts ? part_ml[(at * parts + z) * 2 + 1] : 0.0f;
+        const float big = warp_max(m);
+        const float w = m == -INFINITY ? 0.0f : expf(m - big);
+        const float total = warp_sum(l * w);
+        weight[z] = w / total;
+    }
+    __syncthreads();
+    const float* mine = part_out + at * parts * rank;
     for (int d = threadIdx.x; d < rank; d += blockDim.x) {
         float o = 0.0f;
-        for (int z = 0; z < parts; z++)
-            if (ml[2 * z] != -INFINITY) o = fmaf(part_out[(at * parts + z) * rank + d], expf(ml[2 * z] - big), o);
-        if (out_bf16) reinterpret_cast<bf16*>(out)[at * rank + d] = __float2bfloat16_rn(o / total);
-        else reinterpret_cast<float*>(out)[at * rank + d] = o / total;
+#pragma unroll 8
+        for (int z = 0; z < parts; z++) o = fmaf(mine[(long)z * rank + d], weight[z], o);
+        if (out_bf16) reinterpret_cast<bf16*>(out)[at * rank + d] = __float2bfloat16_rn(o);
+        else reinterpret_cast<float*>(out)[at * rank + d] = o;
     }
 }
 
@@ -858,7 +864,7 @@ extern "C" int mllm_sequence_latent_attention_tiled(const LatentTiledParams* par
     const int rows = p.HB * p.TQ;
     if (p.HB <= 0 || p.TQ <= 0 || (rows != 32 && rows != 16) || 128 % p.TQ != 0) return fail("latent_attention_tiled: a block takes 32 or 16 rows");
     if (p.tiles == nullptr && p.TQ != 1) return fail("latent_attention_tiled: single tokens come one per block");
-    if (p.parts < 1 || (p.parts > 1 && (p.tiles != nullptr || p.part_out == nullptr || p.part_ml == nullptr)))
+    if (p.parts < 1 || p.parts > 32 || (p.parts > 1 && (p.tiles != nullptr || p.part_out == nullptr || p.part_ml == nullptr)))
         return fail("latent_attention_tiled: parts are for single tokens and need scratch");
     const int element_bytes = dtype == DT_F32 ? 4 : 2;
     p.key_buffers = latent_tiled_shared_bytes(rows, row_width, element_bytes, 2) <= 220 * 1024 ? 2 : 1;
