@@ -959,12 +959,11 @@ def latent_attention_tiled_takes(pages, rank, rot) -> bool:
 
 
 def latent_heads_per_block(heads: int) -> int:
-    """Heads of one block of 32 rows in prompt portions: the power of two at or above the number of
-    heads, 32 at most; the block then takes 32 / that many consecutive tokens."""
-    block = 1
-    while block < min(heads, LATENT_TILE_ROWS):
-        block *= 2
-    return block
+    """Heads of one block of 32 rows in prompt portions: the power of two (32 at most) that leaves
+    the fewest rows for heads that do not exist, the larger one on a tie; the block then takes
+    32 / that many consecutive tokens.  (12 heads: 4 a block and 8 tokens, no row idle; 16 a block
+    would idle a quarter of the rows, and a cached row read thrice costs less than that.)"""
+    return min((32, 16, 8, 4, 2, 1), key=lambda block: (-(-heads // block) * block, -block))
 
 
 def latent_attention_tiled(out, q_eff, pages, block_table, positions, token_item, heads, rank, rot, page_size, scale,
