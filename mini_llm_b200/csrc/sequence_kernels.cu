@@ -553,7 +553,7 @@ struct LatentTiledParams {
     const float* q_eff;            // [T, heads * (rank + rot)]
     const void* pages;
     const int* block_table; const int* positions; const int* token_item; const int* tiles;
-    int max_blocks, page_size, n_tokens, heads, rank, rot, TQ, HB, parts, keys_per_part;
+    int max_blocks, page_size, n_tokens, heads, rank, rot, TQ, HB, parts;
     float scale;
     int out_bf16;                  // `out` holds bfloat16 (the expansion that follows then runs on the tensor cores)
     int key_buffers;               // 2: the next block of cached rows is copied (cp.async) while this one is used; 1: no room for that

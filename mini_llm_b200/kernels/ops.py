@@ -941,7 +941,7 @@ def latent_attention_plain(out, q_eff, pages, block_table, positions, token_item
 class _LatentTiledParams(ctypes.Structure):
     _fields_ = [("out", P), ("part_out", P), ("part_ml", P), ("q_eff", P), ("pages", P), ("block_table", P),
                 ("positions", P), ("token_item", P), ("tiles", P), ("max_blocks", I), ("page_size", I), ("n_tokens", I),
-                ("heads", I), ("rank", I), ("rot", I), ("TQ", I), ("HB", I), ("parts", I), ("keys_per_part", I),
+                ("heads", I), ("rank", I), ("rot", I), ("TQ", I), ("HB", I), ("parts", I),
                 ("scale", F), ("out_bf16", I), ("key_buffers", I)]
 
 

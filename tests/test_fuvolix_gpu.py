@@ -320,3 +320,22 @@ def test_latent_attention_in_tiles_against_the_plain_kernel(heads, rank, rot):
                                    token_item[last].contiguous(), heads, rank, rot, page_size, 0.4, parts=parts,
                                    scratch=scratch)
         torch.testing.assert_close(got, want[last], rtol=2e-5, atol=2e-5)
+
+
+def test_bfloat16_with_sizes_no_fast_kernel_takes(tmp_path):
+    """A width that is no multiple of 8, a latent that is no multiple of 8, key sizes of 5 and 6: every
+    product, the attention and the memories fall back to kernels that take any size, in bfloat16
+    too, for prompts, portions and single tokens."""
+    raw = fx.config([fx.latent(heads=3, dim=10, rot_dim=6, vdim=14, kv_rank=22, ff=52), fx.mlstm(heads=2, dim=6, vdim=10),
+                     fx.lightning(heads=3, dim=5, vdim=7, ff=36), fx.latent(heads=5, dim=4, rot_dim=2, vdim=6, kv_rank=13, dims=2)],
+                    width=100, groups=5, vocab=203, taps=5)
+    folder = fx.make_model(str(tmp_path / "m"), raw, seed=29, matrix_scale=2.0)
+    requests = {"a": random_tokens(61, 150, 203), "b": random_tokens(62, 3, 203), "c": random_tokens(63, 40, 203)}
+    bound = max(bf16_atol(fx.plain_logits(folder, tokens)) for tokens in requests.values())
+    engine = engine_for(folder, dtype="bfloat16")
+    check(engine, folder, requests, schedule_whole(requests), atol=bound)
+    check(engine, folder, requests, schedule_mixed(requests, {"a": 130, "b": 2, "c": 33}, max_live=3), atol=bound)
+    chosen = {kernel for key, kernel in engine.kernels.choices.items() if key[0] in ("latent_attention", "head_linear", "linear")}
+    assert chosen == {"latent_attention_plain", "head_linear_plain", "linear_plain"}
+    engine32 = engine_for(folder)
+    check(engine32, folder, requests, schedule_portions(requests))
