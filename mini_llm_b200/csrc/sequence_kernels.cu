@@ -578,7 +578,7 @@ __device__ __forceinline__ void unpack4(const uint2& c, float* v) {
     v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
 }
 
-template <typename T, int R, int RPT, int CT>
+template <typename T, int R, int RPT, int CT, int BK>
 __global__ void __launch_bounds__(256)
 latent_attention_tiled_kernel(LatentTiledParams p) {
     dependents_may_start();
@@ -586,7 +586,9 @@ latent_attention_tiled_kernel(LatentTiledParams p) {
     typedef typename Chunk4<T>::type chunk_t;
     // R rows a block: 32, or 16 for single tokens of models with up to 16 heads (no thread then
     // computes for a row that is nobody's); RW rows per warp in the softmax, RP per thread in the scores
-    constexpr int BK = 32, CG = 256 / (R / RPT), RW = R / 8, RP = R / 16;
+    // BK keys a block: 32, or 64 for prompt portions where they fit (a thread then computes 4 x 2
+    // scores from six loads instead of 2 x 2 from four)
+    constexpr int CG = 256 / (R / RPT), RW = R / 8, RP = R / 16;
     extern __shared__ __align__(16) unsigned char raw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int row_width = p.rank + p.rot, ld = row_width + 4;
@@ -680,7 +682,27 @@ latent_attention_tiled_kernel(LatentTiledParams p) {
         __syncthreads();                                            // (Qs and row_position are written, too)
         // scores: rows rp, rp + 16 against keys jp, jp + 16
         {
-            if constexpr (RP == 2) {
+            if constexpr (BK == 64) {
+                // rows rq, rq + 8, rq + 16, rq + 24 against keys jq, jq + 32
+                const int rq = tid >> 5, jq = tid & 31;
+                float sa[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sb[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                for (int d = 0; d < row_width; d += 4) {
+                    float ka[4], kb[4];
+                    unpack4(*reinterpret_cast<const chunk_t*>(Ks + jq * ld + d), ka);
+                    unpack4(*reinterpret_cast<const chunk_t*>(Ks + (jq + 32) * ld + d), kb);
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const float4 q4 = *reinterpret_cast<const float4*>(Qs + (rq + 8 * u) * ld + d);
+                        sa[u] = fmaf(q4.x, ka[0], fmaf(q4.y, ka[1], fmaf(q4.z, ka[2], fmaf(q4.w, ka[3], sa[u]))));
+                        sb[u] = fmaf(q4.x, kb[0], fmaf(q4.y, kb[1], fmaf(q4.z, kb[2], fmaf(q4.w, kb[3], sb[u]))));
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    Ss[(rq + 8 * u) * (BK + 1) + jq] = sa[u];
+                    Ss[(rq + 8 * u) * (BK + 1) + jq + 32] = sb[u];
+                }
+            } else if constexpr (RP == 2) {
                 float s00 = 0.0f, s01 = 0.0f, s10 = 0.0f, s11 = 0.0f;
                 for (int d = 0; d < row_width; d += 4) {
                     const float4 qa = *reinterpret_cast<const float4*>(Qs + rp * ld + d);
@@ -715,18 +737,26 @@ latent_attention_tiled_kernel(LatentTiledParams p) {
         // softmax, online: warp w owns rows RW w .. RW w + RW - 1, a lane a key
 #pragma unroll
         for (int i = 0; i < RW; i++) {
-            const int r = warp * RW + i, key = k0 + lane;
-            const bool seen = key < key_end && key <= row_position[r];
-            const float sc = seen ? Ss[r * (BK + 1) + lane] * p.scale : -INFINITY;
-            const float m_new = fmaxf(m_row[i], warp_max(sc));
-            float c = 0.0f, e = 0.0f;
-            if (m_new != -INFINITY) {
-                c = expf(m_row[i] - m_new);
-                e = expf(sc - m_new);
+            const int r = warp * RW + i;
+            float sc[BK / 32], top = -INFINITY;
+#pragma unroll
+            for (int u = 0; u < BK / 32; u++) {
+                const int key = k0 + lane + 32 * u;
+                const bool seen = key < key_end && key <= row_position[r];
+                sc[u] = seen ? Ss[r * (BK + 1) + lane + 32 * u] * p.scale : -INFINITY;
+                top = fmaxf(top, sc[u]);
             }
-            l_row[i] = l_row[i] * c + warp_sum(e);
+            const float m_new = fmaxf(m_row[i], warp_max(top));
+            float c = 0.0f, total = 0.0f;
+            if (m_new != -INFINITY) c = expf(m_row[i] - m_new);
+#pragma unroll
+            for (int u = 0; u < BK / 32; u++) {
+                const float e = m_new != -INFINITY ? expf(sc[u] - m_new) : 0.0f;
+                Ss[r * (BK + 1) + lane + 32 * u] = e;
+                total += e;
+            }
+            l_row[i] = l_row[i] * c + warp_sum(total);
             m_row[i] = m_new;
-            Ss[r * (BK + 1) + lane] = e;
             if (lane == 0) factor[r] = c;
         }
         __syncthreads();
@@ -827,22 +857,28 @@ __global__ void latent_merge_kernel(void* __restrict__ out, int out_bf16, const 
     }
 }
 
-static size_t latent_tiled_shared_bytes(int rows, int row_width, int element_bytes, int key_buffers) {
+static size_t latent_tiled_shared_bytes(int rows, int row_width, int element_bytes, int key_buffers, int keys = 32) {
     const size_t ld = (size_t)row_width + 4;
-    return rows * ld * 4 + rows * 33 * 4 + 2 * rows * 4 + key_buffers * 32 * ld * (size_t)element_bytes;
+    return rows * ld * 4 + rows * (keys + 1) * 4 + 2 * rows * 4 + key_buffers * keys * ld * (size_t)element_bytes;
 }
 
-template <typename T, int R, int RPT, int CT>
+template <typename T, int R, int RPT, int CT, int BK = 32>
 static int launch_latent_tiled(const LatentTiledParams& p, dim3 grid, size_t shared, cudaStream_t s) {
     if (shared > 48 * 1024)
-        cudaFuncSetAttribute(latent_attention_tiled_kernel<T, R, RPT, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-    launch_kernel(g_dependent_launch != 0, latent_attention_tiled_kernel<T, R, RPT, CT>, dim3(grid), dim3(256), shared, s, p);
+        cudaFuncSetAttribute(latent_attention_tiled_kernel<T, R, RPT, CT, BK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    launch_kernel(g_dependent_launch != 0, latent_attention_tiled_kernel<T, R, RPT, CT, BK>, dim3(grid), dim3(256), shared, s, p);
     return check_launch("latent_attention_tiled_kernel");
 }
 
 // (a thread's accumulators: RPT rows x 8 CT latent columns; 256 threads cover R rows x the latent)
 template <typename T>
-static int pick_latent_tiled(const LatentTiledParams& p, int rows, dim3 grid, size_t shared, cudaStream_t s) {
+static int pick_latent_tiled(const LatentTiledParams& p, int rows, int keys, dim3 grid, size_t shared, cudaStream_t s) {
+    if (keys == 64) {
+        if (p.rank <= 128) return launch_latent_tiled<T, 32, 2, 1, 64>(p, grid, shared, s);
+        if (p.rank <= 256) return launch_latent_tiled<T, 32, 4, 1, 64>(p, grid, shared, s);
+        if (p.rank <= 512) return launch_latent_tiled<T, 32, 8, 1, 64>(p, grid, shared, s);
+        return launch_latent_tiled<T, 32, 8, 2, 64>(p, grid, shared, s);
+    }
     if (rows == 16) {
         if (p.rank <= 128) return launch_latent_tiled<T, 16, 1, 1>(p, grid, shared, s);
         if (p.rank <= 256) return launch_latent_tiled<T, 16, 2, 1>(p, grid, shared, s);
@@ -867,14 +903,17 @@ extern "C" int mllm_sequence_latent_attention_tiled(const LatentTiledParams* par
     if (p.parts < 1 || p.parts > 32 || (p.parts > 1 && (p.tiles != nullptr || p.part_out == nullptr || p.part_ml == nullptr)))
         return fail("latent_attention_tiled: parts are for single tokens and need scratch");
     const int element_bytes = dtype == DT_F32 ? 4 : 2;
-    p.key_buffers = latent_tiled_shared_bytes(rows, row_width, element_bytes, 2) <= 220 * 1024 ? 2 : 1;
-    const size_t shared = latent_tiled_shared_bytes(rows, row_width, element_bytes, p.key_buffers);
+    // prompt portions take 64 keys a block where two such blocks, or one, fit beside the queries
+    int keys = 32;
+    if (p.tiles != nullptr && rows == 32 && latent_tiled_shared_bytes(rows, row_width, element_bytes, 1, 64) <= 220 * 1024) keys = 64;
+    p.key_buffers = latent_tiled_shared_bytes(rows, row_width, element_bytes, 2, keys) <= 220 * 1024 ? 2 : 1;
+    const size_t shared = latent_tiled_shared_bytes(rows, row_width, element_bytes, p.key_buffers, keys);
     if (shared > 220 * 1024) return fail("latent_attention_tiled: the rows do not fit in shared memory");
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(p.tiles != nullptr ? n_units * (128 / p.TQ) : n_units, (p.heads + p.HB - 1) / p.HB, p.parts);
     int rc;
-    if (dtype == DT_F32) rc = pick_latent_tiled<float>(p, rows, grid, shared, s);
-    else if (dtype == DT_BF16) rc = pick_latent_tiled<bf16>(p, rows, grid, shared, s);
+    if (dtype == DT_F32) rc = pick_latent_tiled<float>(p, rows, keys, grid, shared, s);
+    else if (dtype == DT_BF16) rc = pick_latent_tiled<bf16>(p, rows, keys, grid, shared, s);
     else return fail("latent_attention_tiled: unknown dtype");
     if (rc != 0 || p.parts == 1) return rc;
     launch_kernel(g_dependent_launch != 0, latent_merge_kernel, dim3((unsigned)((long)n_units * p.heads)), dim3(128), 0, s, p.out, p.out_bf16, p.part_out, p.part_ml, p.parts, p.rank);
