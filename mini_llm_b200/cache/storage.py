@@ -61,6 +61,12 @@ class CompositeLayerCache(LayerCache):
     def of(self, role: str):
         return self.by_role.get(role) or LayerCache()
 
+    def sub(self, prefix: str):
+        """The caches whose role starts with ``prefix.``, under the rest of their names: what a part
+        that is itself put together from parts hands on to each of them."""
+        head = prefix + "."
+        return CompositeLayerCache({role[len(head):]: view for role, view in self.by_role.items() if role.startswith(head)})
+
 
 class CacheStorage:
     def __init__(self, manager, order, dtype: torch.dtype, device, max_items: int, poison: float | None = None):
@@ -84,6 +90,7 @@ class CacheStorage:
                 fill = 0.0 if poison is None else poison
                 self.keys[group.index] = torch.full(shape, fill, dtype=dtype, device=device)
                 if group.need.has_values:
+                    shape = (*shape[:4], group.need.value_size or group.need.head_size)
                     self.values[group.index] = torch.full(shape, fill, dtype=dtype, device=device)
                 self.block_tables[group.index] = torch.zeros((self.max_items, group.max_blocks), dtype=torch.int32,
                                                              device=device)

@@ -1,0 +1,733 @@
+// Kernels of layers that run a softmax attention beside a linear recurrence, and of routed
+// feed-forwards:
+//   rotary_store      rotary positions (interleaved pairs, a frequency table, an amplitude) on the
+//                     step's queries and keys, and the keys and values into their cache pages
+//   capped_attention  causal attention over the paged cache with keys and values of different
+//                     sizes, a tanh cap on the scores and query heads that share a key/value head;
+//                     scores, softmax and the weighted sum of values in 32-bit
+//   linear_recurrence S <- a_t S + k_t u_t^T per head with a_t and the write strength b_t per token:
+//                     u_t = b_t v_t (state-space form) or u_t = b_t (v_t - (a_t S)^T k_t) (delta rule);
+//                     read out after the write; gates, decays and the state in 32-bit
+//   route / expert_up / expert_down   a router with sigmoid scores and the largest few experts per
+//                     token, gated experts fed the token times its score, a shared expert with an
+//                     output gate
+//   scaled_add        x += a * u + b * v on the 32-bit residual stream
+// Every kernel is templated on the element type of the activations (float: the true 32-bit path;
+// bfloat16: the serving path) and is launched as a programmatic dependent of the kernel before it.
+#include "common.cuh"
+
+MLLM_DEFINE_ERROR_API(mllm_hybrid)
+
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z))); }
+
+// ---------------------------------------------------------------------------
+// Rotary positions and the cache store.  A row of `qkv` holds [q: heads * dim | k: kv_heads * dim |
+// v: kv_heads * vdim] at the given column offsets.  Among the first rot_dims entries of every
+// query and key head, (x[2i], x[2i+1]) turns by position * inv_freq[i]; cosine and sine are
+// multiplied by `amplitude`.  Angles are taken in 64-bit, once per token and pair.  Queries and
+// keys are rotated in place; keys and values then go to the token's place in the pages.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void rotary_store_kernel(T* __restrict__ qkv, long ld, int k_off, int v_off, int heads, int kv_heads, int dim,
+                                    int vdim, int rot_dims, const double* __restrict__ inv_freq, double amplitude,
+                                    const int* __restrict__ positions, const int* __restrict__ token_item,
+                                    const int* __restrict__ block_table, int max_blocks, int page_size,
+                                    T* __restrict__ k_pages, T* __restrict__ v_pages, int writes) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
+    extern __shared__ float turn[];              // [rot_dims / 2][2]: cosine, sine
+    const int t = blockIdx.x;
+    const int p = positions[t];
+    const int half = rot_dims / 2;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        double s, c;
+        sincos((double)p * inv_freq[i], &s, &c);
+        turn[2 * i] = (float)(c * amplitude);
+        turn[2 * i + 1] = (float)(s * amplitude);
+    }
+    __syncthreads();
+    T* row = qkv + (long)t * ld;
+    const int page = block_table[(long)token_item[t] * max_blocks + p / page_size];
+    const long slot = (long)page * page_size + (p % page_size);
+    // queries and keys: pairs of the rotated part, then what passes unchanged
+    const int pairs_per_head = dim / 2 + (dim & 1);
+    for (int u = threadIdx.x; u < (heads + kv_heads) * pairs_per_head; u += blockDim.x) {
+        const int head = u / pairs_per_head, i = u % pairs_per_head;
+        const bool is_key = head >= heads;
+        T* x = is_key ? row + k_off + (long)(head - heads) * dim : row + (long)head * dim;
+        float a = to_f32(x[2 * i]);
+        float b = 2 * i + 1 < dim ? to_f32(x[2 * i + 1]) : 0.0f;
+        if (i < half) {
+            const float c = turn[2 * i], s = turn[2 * i + 1];
+            const float ra = a * c - b * s, rb = b * c + a * s;
+            a = ra, b = rb;
+            x[2 * i] = from_f32<T>(a);
+            x[2 * i + 1] = from_f32<T>(b);
+        }
+        if (is_key && writes) {
+            T* dst = k_pages + (slot * kv_heads + (head - heads)) * dim;
+            dst[2 * i] = from_f32<T>(a);
+            if (2 * i + 1 < dim) dst[2 * i + 1] = from_f32<T>(b);
+        }
+    }
+    if (writes)
+        for (int c = threadIdx.x; c < kv_heads * vdim; c += blockDim.x)
+            v_pages[slot * kv_heads * vdim + c] = row[v_off + c];
+}
+
+extern "C" int mllm_hybrid_rotary_store(void* qkv, long ld, int k_off, int v_off, int heads, int kv_heads, int dim, int vdim,
+                                        int rot_dims, const double* inv_freq, double amplitude, const int* positions,
+                                        const int* token_item, const int* block_table, int max_blocks, int page_size,
+                                        void* k_pages, void* v_pages, int writes, int n_tokens, int dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (rot_dims < 0 || rot_dims % 2 != 0 || rot_dims > dim) return fail("rotary_store: an even number of at most dim entries is rotated");
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t shared = (size_t)(rot_dims + 2) * sizeof(float);
+    if (dtype == DT_F32)
+        launch_kernel(g_dependent_launch != 0, rotary_store_kernel<float>, dim3(n_tokens), dim3(128), shared, s, (float*)qkv, ld,
+                      k_off, v_off, heads, kv_heads, dim, vdim, rot_dims, inv_freq, amplitude, positions, token_item, block_table,
+                      max_blocks, page_size, (float*)k_pages, (float*)v_pages, writes);
+    else if (dtype == DT_BF16)
+        launch_kernel(g_dependent_launch != 0, rotary_store_kernel<bf16>, dim3(n_tokens), dim3(128), shared, s, (bf16*)qkv, ld,
+                      k_off, v_off, heads, kv_heads, dim, vdim, rot_dims, inv_freq, amplitude, positions, token_item, block_table,
+                      max_blocks, page_size, (bf16*)k_pages, (bf16*)v_pages, writes);
+    else
+        return fail("rotary_store: unknown dtype");
+    return check_launch("rotary_store_kernel");
+}
+
+// ---------------------------------------------------------------------------
+// Causal attention with capped scores, one block per (token, head): the plain form, which takes
+// every size.  score = cap * tanh((q . k) * scale / cap) (cap <= 0: no cap); the query at position
+// p sees keys max(0, p - window + 1) .. p (window <= 0: all).  Four warps take the keys in turn,
+// each with an online softmax; their states are merged in a fixed order.
+// ---------------------------------------------------------------------------
+constexpr int CAP_MAX_HEAD = 256;
+
+__device__ __forceinline__ float capped(float s, float cap, float inv_cap) { return cap > 0.0f ? cap * tanhf(s * inv_cap) : s; }
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+capped_attention_plain_kernel(T* __restrict__ out, long ld_out, const T* __restrict__ q, long ld_q,
+                              const T* __restrict__ k_pages, const T* __restrict__ v_pages,
+                              const int* __restrict__ block_table, int max_blocks, const int* __restrict__ positions,
+                              const int* __restrict__ token_item, int n_heads, int n_kv_heads, int dim, int vdim,
+                              int page_size, float scale, float cap, int window) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
+    constexpr int R = CAP_MAX_HEAD / 32;
+    const int t = blockIdx.x, h = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int p = positions[t];
+    const int* bt = block_table + (long)token_item[t] * max_blocks;
+    const int hk = h / (n_heads / n_kv_heads);
+    const float inv_cap = cap > 0.0f ? 1.0f / cap : 0.0f;
+    float qr[R], acc[R];
+#pragma unroll
+    for (int i = 0; i < R; i++) {
+        const int d = lane + 32 * i;
+        qr[i] = d < dim ? to_f32(q[(long)t * ld_q + (long)h * dim + d]) : 0.0f;
+        acc[i] = 0.0f;
+    }
+    float m = -INFINITY, l = 0.0f;
+    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    for (int j = lo + warp; j <= p; j += 4) {
+        const long slot = (long)bt[j / page_size] * page_size + (j % page_size);
+        const T* kr = k_pages + (slot * n_kv_heads + hk) * dim;
+        const T* vr = v_pages + (slot * n_kv_heads + hk) * vdim;
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < R; i++) {
+            const int d = lane + 32 * i;
+            if (d < dim) s = fmaf(qr[i], to_f32(kr[d]), s);
+        }
+        s = capped(warp_sum(s) * scale, cap, inv_cap);
+        const float m_new = fmaxf(m, s);
+        const float c = expf(m - m_new), e = expf(s - m_new);
+        l = l * c + e;
+#pragma unroll
+        for (int i = 0; i < R; i++) {
+            const int d = lane + 32 * i;
+            if (d < vdim) acc[i] = acc[i] * c + e * to_f32(vr[d]);
+        }
+        m = m_new;
+    }
+    __shared__ float sm_m[4], sm_l[4];
+    __shared__ float sm_acc[4][CAP_MAX_HEAD];
+    if (lane == 0) sm_m[warp] = m, sm_l[warp] = l;
+#pragma unroll
+    for (int i = 0; i < R; i++) {
+        const int d = lane + 32 * i;
+        if (d < vdim) sm_acc[warp][d] = acc[i];
+    }
+    __syncthreads();
+    const float big = fmaxf(fmaxf(sm_m[0], sm_m[1]), fmaxf(sm_m[2], sm_m[3]));
+    float total = 0.0f, wgt[4];
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+        wgt[w] = sm_m[w] == -INFINITY ? 0.0f : expf(sm_m[w] - big);
+        total += sm_l[w] * wgt[w];
+    }
+    for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
+        float o = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) o += sm_acc[w][d] * wgt[w];
+        out[(long)t * ld_out + (long)h * vdim + d] = from_f32<T>(o / total);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// The same attention in tiles, for steps with prompt portions.  A block takes ROWS consecutive
+// tokens of the step and HC query heads of one key/value head: up to 16 (token, head) rows, two
+// a warp.  Tokens of one request that lie side by side share every block of 32 cached keys and
+// values, which the block brings into shared memory once, in 32-bit.  Within a warp the lanes take
+// the 32 keys of a block for the scores, and the value entries for the weighted sum; scores,
+// maxima, sums and weights are 32-bit.  A tile whose tokens belong to several requests takes the
+// requests one after the other.
+// ---------------------------------------------------------------------------
+constexpr int TILE_KEYS = 32;
+constexpr int TILE_ROWS = 16;          // (token, head) rows a block
+constexpr int TILE_WARPS = 8;
+constexpr int TILE_VPL = CAP_MAX_HEAD / 32;
+
+template <typename T>
+__global__ void __launch_bounds__(TILE_WARPS * 32)
+capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restrict__ q, long ld_q,
+                              const T* __restrict__ k_pages, const T* __restrict__ v_pages,
+                              const int* __restrict__ block_table, int max_blocks, const int* __restrict__ positions,
+                              const int* __restrict__ token_item, int n_tokens, int n_heads, int n_kv_heads, int dim,
+                              int vdim, int page_size, float scale, float cap, int window, int tokens_per_block,
+                              int heads_per_block) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
+    extern __shared__ float shared[];
+    const int kd = dim + 4;                                  // padded key row: lanes read rows, four entries at a time
+    float* q_rows = shared;                                  // [TILE_ROWS][dim]
+    float* keys = q_rows + TILE_ROWS * dim;                  // [TILE_KEYS][kd]
+    float* values = keys + TILE_KEYS * kd;                   // [TILE_KEYS][vdim]
+    float* weights = values + TILE_KEYS * vdim;              // [TILE_WARPS][2][TILE_KEYS]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int group = n_heads / n_kv_heads;
+    const int chunks = (group + heads_per_block - 1) / heads_per_block;
+    const int hk = blockIdx.y / chunks;
+    const int first_head = hk * group + (blockIdx.y % chunks) * heads_per_block;
+    const int n_heads_here = min(heads_per_block, hk * group + group - first_head);
+    const int first_token = blockIdx.x * tokens_per_block;
+    const int n_tok = min(tokens_per_block, n_tokens - first_token);
+    const int n_rows = n_tok * n_heads_here;
+    const float inv_cap = cap > 0.0f ? 1.0f / cap : 0.0f;
+
+    // this warp's two rows: r = warp and warp + TILE_WARPS; row r = (token r / heads, head r % heads)
+    int row_token[2], row_head[2], row_pos[2], row_item[2];
+    float m[2], l[2], acc[2][TILE_VPL];
+#pragma unroll
+    for (int s = 0; s < 2; s++) {
+        const int r = warp + s * TILE_WARPS;
+        const bool live = r < n_rows;
+        row_token[s] = live ? first_token + r / n_heads_here : -1;
+        row_head[s] = live ? first_head + r % n_heads_here : 0;
+        row_pos[s] = live ? positions[row_token[s]] : -1;
+        row_item[s] = live ? token_item[row_token[s]] : -1;
+        m[s] = -INFINITY, l[s] = 0.0f;
+#pragma unroll
+        for (int i = 0; i < TILE_VPL; i++) acc[s][i] = 0.0f;
+    }
+    for (int u = threadIdx.x; u < n_rows * dim; u += blockDim.x) {
+        const int r = u / dim, d = u % dim;
+        q_rows[r * dim + d] = to_f32(q[(long)(first_token + r / n_heads_here) * ld_q + (long)(first_head + r % n_heads_here) * dim + d]);
+    }
+
+    int run_first = 0;
+    while (run_first < n_tok) {
+        // a run: consecutive tokens of the tile that belong to one request
+        const int item = token_item[first_token + run_first];
+        int run_last = run_first;
+        while (run_last + 1 < n_tok && token_item[first_token + run_last + 1] == item) run_last++;
+        const int p_first = positions[first_token + run_first], p_last = positions[first_token + run_last];
+        const int lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+        const int* bt = block_table + (long)item * max_blocks;
+        for (int base = (lo / TILE_KEYS) * TILE_KEYS; base <= p_last; base += TILE_KEYS) {
+            __syncthreads();                                  // the block before has been read; q_rows are written
+            const int n_keys = min(TILE_KEYS, p_last + 1 - base);
+            for (int u = threadIdx.x; u < n_keys * dim; u += blockDim.x) {
+                const int j = u / dim, d = u % dim, pos = base + j;
+                const long slot = (long)bt[pos / page_size] * page_size + (pos % page_size);
+                keys[j * kd + d] = to_f32(k_pages[(slot * n_kv_heads + hk) * dim + d]);
+            }
+            for (int u = threadIdx.x; u < n_keys * vdim; u += blockDim.x) {
+                const int j = u / vdim, d = u % vdim, pos = base + j;
+                const long slot = (long)bt[pos / page_size] * page_size + (pos % page_size);
+                values[j * vdim + d] = to_f32(v_pages[(slot * n_kv_heads + hk) * vdim + d]);
+            }
+            __syncthreads();
+            bool any = false;
+            float score[2];
+#pragma unroll
+            for (int s = 0; s < 2; s++) {
+                score[s] = -INFINITY;
+                const int pos = base + lane;
+                const int first_seen = (window > 0 && row_pos[s] - window + 1 > 0) ? row_pos[s] - window + 1 : 0;
+                const bool mine = row_item[s] == item;
+                if (mine && base <= row_pos[s] && base + TILE_KEYS > first_seen) any = true;
+                if (mine && lane < n_keys && pos <= row_pos[s] && pos >= first_seen) {
+                    const float* qr = q_rows + (warp + s * TILE_WARPS) * dim;
+                    const float* kr = keys + lane * kd;
+                    float dot = 0.0f;
+                    int d = 0;
+                    for (; d + 4 <= dim; d += 4) {
+                        const float4 a = *reinterpret_cast<const float4*>(qr + d);
+                        const float4 b = *reinterpret_cast<const float4*>(kr + d);
+                        dot = fmaf(a.x, b.x, dot);
+                        dot = fmaf(a.y, b.y, dot);
+                        dot = fmaf(a.z, b.z, dot);
+                        dot = fmaf(a.w, b.w, dot);
+                    }
+                    for (; d < dim; d++) dot = fmaf(qr[d], kr[d], dot);
+                    score[s] = capped(dot * scale, cap, inv_cap);
+                }
+            }
+            if (!any) continue;                               // (uniform in the warp; the barriers are at the loop's head)
+#pragma unroll
+            for (int s = 0; s < 2; s++) {
+                const float block_max = warp_max(score[s]);
+                float rescale = 1.0f, e = 0.0f;
+                if (block_max != -INFINITY) {
+                    const float m_new = fmaxf(m[s], block_max);
+                    rescale = expf(m[s] - m_new);
+                    e = score[s] == -INFINITY ? 0.0f : expf(score[s] - m_new);
+                    m[s] = m_new;
+                }
+                l[s] = l[s] * rescale + warp_sum(e);
+#pragma unroll
+                for (int i = 0; i < TILE_VPL; i++) acc[s][i] *= rescale;
+                weights[(warp * 2 + s) * TILE_KEYS + lane] = e;
+            }
+            __syncwarp();
+            const float* w0 = weights + (warp * 2) * TILE_KEYS;
+            const float* w1 = w0 + TILE_KEYS;
+            for (int j = 0; j < n_keys; j++) {
+                const float a = w0[j], b = w1[j];
+                const float* vr = values + j * vdim;
+#pragma unroll
+                for (int i = 0; i < TILE_VPL; i++) {
+                    const int d = lane + 32 * i;
+                    if (d < vdim) {
+                        const float v = vr[d];
+                        acc[0][i] = fmaf(a, v, acc[0][i]);
+                        acc[1][i] = fmaf(b, v, acc[1][i]);
+                    }
+                }
+            }
+            __syncwarp();
+        }
+        run_first = run_last + 1;
+    }
+#pragma unroll
+    for (int s = 0; s < 2; s++) {
+        if (row_token[s] < 0) continue;
+        const float inv = 1.0f / l[s];
+#pragma unroll
+        for (int i = 0; i < TILE_VPL; i++) {
+            const int d = lane + 32 * i;
+            if (d < vdim) out[(long)row_token[s] * ld_out + (long)row_head[s] * vdim + d] = from_f32<T>(acc[s][i] * inv);
+        }
+    }
+}
+
+static size_t capped_tiled_shared(int dim, int vdim) {
+    return sizeof(float) * ((size_t)TILE_ROWS * dim + (size_t)TILE_KEYS * (dim + 4) + (size_t)TILE_KEYS * vdim + TILE_WARPS * 2 * TILE_KEYS);
+}
+
+extern "C" int mllm_hybrid_capped_attention_tiled_takes(int dim, int vdim) {
+    return dim > 0 && vdim > 0 && dim % 4 == 0 && vdim <= CAP_MAX_HEAD && capped_tiled_shared(dim, vdim) <= 160 * 1024;
+}
+
+template <typename T>
+static int launch_capped_attention(bool tiled, void* out, long ld_out, const void* q, long ld_q, const void* k_pages,
+                                   const void* v_pages, const int* block_table, int max_blocks, const int* positions,
+                                   const int* token_item, int n_tokens, int n_heads, int n_kv_heads, int dim, int vdim,
+                                   int page_size, float scale, float cap, int window, cudaStream_t s) {
+    if (!tiled) {
+        launch_kernel(g_dependent_launch != 0, capped_attention_plain_kernel<T>, dim3(n_tokens, n_heads), dim3(128), 0, s, (T*)out,
+                      ld_out, (const T*)q, ld_q, (const T*)k_pages, (const T*)v_pages, block_table, max_blocks, positions,
+                      token_item, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window);
+        return check_launch("capped_attention_plain_kernel");
+    }
+    const int group = n_heads / n_kv_heads;
+    const int heads_per_block = group < TILE_ROWS ? group : TILE_ROWS;
+    const int tokens_per_block = TILE_ROWS / heads_per_block;
+    const int chunks = (group + heads_per_block - 1) / heads_per_block;
+    const size_t shared = capped_tiled_shared(dim, vdim);
+    cudaError_t e = cudaFuncSetAttribute(capped_attention_tiled_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    if (e != cudaSuccess) return fail("capped_attention: the tiles' shared memory was refused");
+    dim3 grid((n_tokens + tokens_per_block - 1) / tokens_per_block, n_kv_heads * chunks);
+    launch_kernel(g_dependent_launch != 0, capped_attention_tiled_kernel<T>, grid, dim3(TILE_WARPS * 32), shared, s, (T*)out, ld_out,
+                  (const T*)q, ld_q, (const T*)k_pages, (const T*)v_pages, block_table, max_blocks, positions, token_item,
+                  n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, tokens_per_block, heads_per_block);
+    return check_launch("capped_attention_tiled_kernel");
+}
+
+extern "C" int mllm_hybrid_capped_attention(void* out, long ld_out, const void* q, long ld_q, const void* k_pages,
+                                            const void* v_pages, const int* block_table, int max_blocks, const int* positions,
+                                            const int* token_item, int n_tokens, int n_heads, int n_kv_heads, int dim, int vdim,
+                                            int page_size, float scale, float cap, int window, int tiled, int dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (dim <= 0 || dim > CAP_MAX_HEAD || vdim <= 0 || vdim > CAP_MAX_HEAD) return fail("capped_attention: key and value sizes must be in 1..256");
+    if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return fail("capped_attention: heads must be a multiple of the key/value heads");
+    if (n_heads > 65535) return fail("capped_attention: too many heads for one launch");
+    if (tiled && !mllm_hybrid_capped_attention_tiled_takes(dim, vdim)) return fail("capped_attention: the tiles do not take these sizes");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == DT_F32)
+        return launch_capped_attention<float>(tiled != 0, out, ld_out, q, ld_q, k_pages, v_pages, block_table, max_blocks, positions,
+                                              token_item, n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, s);
+    if (dtype == DT_BF16)
+        return launch_capped_attention<bf16>(tiled != 0, out, ld_out, q, ld_q, k_pages, v_pages, block_table, max_blocks, positions,
+                                             token_item, n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, s);
+    return fail("capped_attention: unknown dtype");
+}
+
+// ---------------------------------------------------------------------------
+// Linear recurrence with a matrix state per head, S [dim, vdim] in 32-bit:
+//   a_t = exp(-exp(log_rate[h]) * step_t),  step_t = softplus(gate_a[t, h] + step_bias[h])
+//   state-space form:  b_t = step_t;               u_t = b_t v_t
+//   delta rule:        b_t = sigmoid(gate_b[t, h]); u_t = b_t (v_t - (a_t S)^T k_t)
+//   S <- a_t S + k_t u_t^T;   out_t = S^T q_t (+ skip[h] v_t)
+// Query/key head of head h: h / (heads / qk_heads).  With unit_norm, q and k are divided by
+// sqrt(sum(x^2) + 1e-6) per head first; q is multiplied by q_scale.
+// One block per (entry, head, slice of the value entries): a column of S belongs to LANES threads
+// of one warp, each with DPT rows in registers; both sums over the old column (with k and with q)
+// are taken in one pass, and the read-out follows from them: S_new^T q = a S^T q + u (k . q).
+// The entry's tokens are taken in order, TOK at a time through shared memory.
+// ---------------------------------------------------------------------------
+struct RecurrenceParams {
+    float* out; long ld_out;
+    const void* q; const void* k; const void* v; long ld_q, ld_k, ld_v;
+    const float* gate_a; const float* gate_b; long ld_gate_a, ld_gate_b;
+    const float* log_rate; const float* step_bias; const float* skip;
+    float* state; long state_stride;
+    const int* item_slot; const int* item_offset; const int* item_count;
+    int heads, qk_heads, dim, vdim;
+    float q_scale;
+    int delta, unit_norm, writes;
+};
+
+template <typename T, int DPT, int LANES, int TOK>
+__global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams pp) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
+    constexpr int COLS = 128 / LANES;
+    extern __shared__ float shared[];
+    const int dim = pp.dim, vdim = pp.vdim;
+    float* ks = shared;                         // [TOK][dim]
+    float* qs = ks + TOK * dim;                 // [TOK][dim]
+    float* vs = qs + TOK * dim;                 // [TOK][COLS]
+    float* as = vs + TOK * COLS;                // [TOK] decay
+    float* bs = as + TOK;                       // [TOK] write strength
+    float* kq = bs + TOK;                       // [TOK] k . q
+    const int item = blockIdx.x, head = blockIdx.y;
+    const int count = pp.item_count[item];
+    if (count <= 0) return;
+    const long first = pp.item_offset[item];
+    const int qk_head = head / (pp.heads / pp.qk_heads);
+    const int lane_in = threadIdx.x % LANES, col_local = threadIdx.x / LANES;
+    const int col = blockIdx.z * COLS + col_local;
+    const bool live = col < vdim;
+    float* S = pp.state + (long)pp.item_slot[item] * pp.state_stride + (long)head * dim * vdim;
+    float s[DPT];
+#pragma unroll
+    for (int r = 0; r < DPT; r++) {
+        const int i = lane_in + LANES * r;
+        s[r] = (live && i < dim) ? S[(long)i * vdim + col] : 0.0f;
+    }
+    const float rate = expf(pp.log_rate[head]);
+    const float bias = pp.step_bias[head];
+    const float skip = pp.skip != nullptr ? pp.skip[head] : 0.0f;
+    const T* q = (const T*)pp.q;
+    const T* k = (const T*)pp.k;
+    const T* v = (const T*)pp.v;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int start = 0; start < count; start += TOK) {
+        const int n = min(TOK, count - start);
+        __syncthreads();
+        // a warp stages a token: k and q of the head (unit vectors if asked), their product, the gates
+        for (int tt = warp; tt < n; tt += 4) {
+            const long t = first + start + tt;
+            float sk = 0.0f, sq = 0.0f;
+            for (int d = lane; d < dim; d += 32) {
+                const float kv = to_f32(k[t * pp.ld_k + (long)qk_head * dim + d]);
+                const float qv = to_f32(q[t * pp.ld_q + (long)qk_head * dim + d]);
+                ks[tt * dim + d] = kv, qs[tt * dim + d] = qv;
+                sk = fmaf(kv, kv, sk), sq = fmaf(qv, qv, sq);
+            }
+            float fk = 1.0f, fq = pp.q_scale;
+            if (pp.unit_norm) {
+                fk = 1.0f / sqrtf(warp_sum(sk) + 1e-6f);
+                fq = pp.q_scale / sqrtf(warp_sum(sq) + 1e-6f);
+            }
+            float dot = 0.0f;
+            __syncwarp();
+            for (int d = lane; d < dim; d += 32) {
+                const float kv = ks[tt * dim + d] * fk, qv = qs[tt * dim + d] * fq;
+                ks[tt * dim + d] = kv, qs[tt * dim + d] = qv;
+                dot = fmaf(kv, qv, dot);
+            }
+            dot = warp_sum(dot);
+            if (lane == 0) {
+                const float step = softplus_f(pp.gate_a[t * pp.ld_gate_a + head] + bias);
+                as[tt] = expf(-rate * step);
+                bs[tt] = pp.delta ? sigmoid_f(pp.gate_b[t * pp.ld_gate_b + head]) : step;
+                kq[tt] = dot;
+            }
+        }
+        for (int u = threadIdx.x; u < n * COLS; u += blockDim.x) {
+            const int tt = u / COLS, c = blockIdx.z * COLS + u % COLS;
+            vs[u] = c < vdim ? to_f32(v[(first + start + tt) * pp.ld_v + (long)head * vdim + c]) : 0.0f;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < n; tt++) {
+            const float* kr = ks + tt * dim;
+            const float* qr = qs + tt * dim;
+            float dk = 0.0f, dq = 0.0f;
+#pragma unroll
+            for (int r = 0; r < DPT; r++) {
+                const int i = lane_in + LANES * r;
+                if (i < dim) dk = fmaf(s[r], kr[i], dk), dq = fmaf(s[r], qr[i], dq);
+            }
+#pragma unroll
+            for (int o = LANES / 2; o > 0; o >>= 1) {
+                dk += __shfl_xor_sync(0xffffffffu, dk, o);
+                dq += __shfl_xor_sync(0xffffffffu, dq, o);
+            }
+            const float a = as[tt], b = bs[tt], value = vs[tt * COLS + col_local];
+            const float u = pp.delta ? b * (value - a * dk) : b * value;
+#pragma unroll
+            for (int r = 0; r < DPT; r++) {
+                const int i = lane_in + LANES * r;
+                if (i < dim) s[r] = fmaf(kr[i], u, a * s[r]);
+            }
+            if (live && lane_in == 0)
+                pp.out[(first + start + tt) * pp.ld_out + (long)head * vdim + col] = fmaf(u, kq[tt], a * dq) + skip * value;
+        }
+    }
+    if (pp.writes && live) {
+#pragma unroll
+        for (int r = 0; r < DPT; r++) {
+            const int i = lane_in + LANES * r;
+            if (i < dim) S[(long)i * vdim + col] = s[r];
+        }
+    }
+}
+
+template <typename T, int DPT, int LANES, int TOK>
+static int launch_recurrence(const RecurrenceParams& pp, int n_items, cudaStream_t s) {
+    constexpr int COLS = 128 / LANES;
+    const size_t shared = sizeof(float) * ((size_t)2 * TOK * pp.dim + TOK * COLS + 3 * TOK);
+    dim3 grid(n_items, pp.heads, (pp.vdim + COLS - 1) / COLS);
+    launch_kernel(g_dependent_launch != 0, linear_recurrence_kernel<T, DPT, LANES, TOK>, grid, dim3(128), shared, s, pp);
+    return check_launch("linear_recurrence_kernel");
+}
+
+template <typename T>
+static int pick_recurrence(const RecurrenceParams& pp, int n_items, cudaStream_t s) {
+    if (pp.dim <= 32) return launch_recurrence<T, 8, 4, 16>(pp, n_items, s);
+    if (pp.dim <= 64) return launch_recurrence<T, 16, 4, 16>(pp, n_items, s);
+    if (pp.dim <= 128) return launch_recurrence<T, 32, 4, 16>(pp, n_items, s);
+    if (pp.dim <= 256) return launch_recurrence<T, 32, 8, 16>(pp, n_items, s);
+    return launch_recurrence<T, 32, 32, 4>(pp, n_items, s);
+}
+
+extern "C" int mllm_hybrid_linear_recurrence(const RecurrenceParams* params, int n_items, int dtype, void* stream) {
+    if (n_items <= 0) return 0;
+    const RecurrenceParams& pp = *params;
+    if (pp.dim <= 0 || pp.dim > 1024 || pp.vdim <= 0) return fail("linear_recurrence: the key size must be in 1..1024");
+    if (pp.qk_heads <= 0 || pp.heads % pp.qk_heads != 0) return fail("linear_recurrence: heads must be a multiple of the query/key heads");
+    if (pp.heads > 65535) return fail("linear_recurrence: too many heads for one launch");
+    if (pp.delta && pp.gate_b == nullptr) return fail("linear_recurrence: the delta rule needs its write gates");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == DT_F32) return pick_recurrence<float>(pp, n_items, s);
+    if (dtype == DT_BF16) return pick_recurrence<bf16>(pp, n_items, s);
+    return fail("linear_recurrence: unknown dtype");
+}
+
+// ---------------------------------------------------------------------------
+// Routed feed-forward, the plain form: every (token, chosen expert) pair by itself.
+//   route        per token: z = W_router x in 32-bit, s = sigmoid(z); the `top` experts with the
+//                largest s (the lower index wins a tie) with s as the weight of their INPUT; if
+//                there is a shared expert, one more pair: expert `n_experts`, input weight 1,
+//                output weight sigmoid(w_shared_gate . x)
+//   expert_up    act[pair, f] = silu(W_gate[e] x') * (W_up[e] x') with x' = weight * x
+//   expert_down  hidden[t] += sum over the token's pairs of out_weight * W_down[e] act[pair]
+// Experts are named by a table of pointers (gate, up, down) and inner sizes, so that experts of
+// different sizes (the shared one) go through the same kernels.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+route_kernel(const T* __restrict__ x, long ld_x, const T* __restrict__ router, const T* __restrict__ shared_gate, int width,
+             int n_experts, int top, int pairs, int* __restrict__ choice, float* __restrict__ in_weight,
+             float* __restrict__ out_weight) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
+    extern __shared__ float shared[];
+    float* row = shared;                       // [width]
+    float* score = row + width;                // [n_experts + 1]
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) row[c] = to_f32(x[(long)t * ld_x + c]);
+    __syncthreads();
+    for (int e = warp; e < n_experts + (shared_gate != nullptr ? 1 : 0); e += 4) {
+        const T* w = e < n_experts ? router + (long)e * width : shared_gate;
+        float z = 0.0f;
+        for (int c = lane; c < width; c += 32) z = fmaf(to_f32(w[c]), row[c], z);
+        z = warp_sum(z);
+        if (lane == 0) score[e] = sigmoid_f(z);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int k = 0; k < top; k++) {
+            int best = -1;
+            float best_score = -1.0f;
+            for (int e = 0; e < n_experts; e++)
+                if (score[e] > best_score) best = e, best_score = score[e];
+            if (best < 0) best = 0, best_score = score[0];      // (scores that are no numbers)
+            choice[(long)t * pairs + k] = best;
+            in_weight[(long)t * pairs + k] = best_score;
+            out_weight[(long)t * pairs + k] = 1.0f;
+            score[best] = -2.0f;
+        }
+        if (shared_gate != nullptr) {
+            choice[(long)t * pairs + top] = n_experts;
+            in_weight[(long)t * pairs + top] = 1.0f;
+            out_weight[(long)t * pairs + top] = score[n_experts];
+        }
+    }
+}
+
+constexpr int UP_FEATURES = 32;                // inner features a block of expert_up takes (four a warp)
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+expert_up_kernel(T* __restrict__ act, long ld_act, const T* __restrict__ x, long ld_x, const int* __restrict__ choice,
+                 const float* __restrict__ in_weight, const long long* __restrict__ gate_of, const long long* __restrict__ up_of,
+                 const int* __restrict__ inner_of, int width, int pairs) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
+    extern __shared__ float row[];             // [width]: the token times its weight, rounded as an activation
+    const int pair = blockIdx.x, t = pair / pairs;
+    const int e = choice[pair];
+    const int inner = inner_of[e];
+    const int first = blockIdx.y * UP_FEATURES;
+    if (first >= inner) return;
+    const float weight = in_weight[pair];
+    for (int c = threadIdx.x; c < width; c += blockDim.x)
+        row[c] = to_f32(from_f32<T>(weight * to_f32(x[(long)t * ld_x + c])));
+    __syncthreads();
+    const T* gate = (const T*)gate_of[e];
+    const T* up = (const T*)up_of[e];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int f = first + warp; f < min(first + UP_FEATURES, inner); f += 8) {
+        const T* g = gate + (long)f * width;
+        const T* u = up + (long)f * width;
+        float zg = 0.0f, zu = 0.0f;
+        for (int c = lane; c < width; c += 32) {
+            zg = fmaf(to_f32(g[c]), row[c], zg);
+            zu = fmaf(to_f32(u[c]), row[c], zu);
+        }
+        zg = warp_sum(zg), zu = warp_sum(zu);
+        if (lane == 0) act[(long)pair * ld_act + f] = from_f32<T>(silu_f(zg) * zu);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+expert_down_kernel(float* __restrict__ hidden, long ld_hidden, const T* __restrict__ act, long ld_act,
+                   const int* __restrict__ choice, const float* __restrict__ out_weight, const long long* __restrict__ down_of,
+                   const int* __restrict__ inner_of, int width, int pairs) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int c = blockIdx.y * 8 + warp; c < width; c += gridDim.y * 8) {
+        float total = 0.0f;
+        for (int k = 0; k < pairs; k++) {
+            const long pair = (long)t * pairs + k;
+            const int e = choice[pair];
+            const int inner = inner_of[e];
+            const T* w = (const T*)down_of[e] + (long)c * inner;
+            const T* a = act + pair * ld_act;
+            float z = 0.0f;
+            for (int f = lane; f < inner; f += 32) z = fmaf(to_f32(w[f]), to_f32(a[f]), z);
+            total = fmaf(out_weight[pair], warp_sum(z), total);
+        }
+        if (lane == 0) hidden[(long)t * ld_hidden + c] += total;
+    }
+}
+
+extern "C" int mllm_hybrid_route(const void* x, long ld_x, const void* router, const void* shared_gate, int width, int n_experts,
+                                 int top, int* choice, float* in_weight, float* out_weight, int n_tokens, int dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (top <= 0 || top > n_experts) return fail("route: every token takes between one and all experts");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int pairs = top + (shared_gate != nullptr ? 1 : 0);
+    const size_t shared = sizeof(float) * ((size_t)width + n_experts + 1);
+    if (shared > 48 * 1024) return fail("route: the token and the scores do not fit shared memory");
+    if (dtype == DT_F32)
+        launch_kernel(g_dependent_launch != 0, route_kernel<float>, dim3(n_tokens), dim3(128), shared, s, (const float*)x, ld_x,
+                      (const float*)router, (const float*)shared_gate, width, n_experts, top, pairs, choice, in_weight, out_weight);
+    else if (dtype == DT_BF16)
+        launch_kernel(g_dependent_launch != 0, route_kernel<bf16>, dim3(n_tokens), dim3(128), shared, s, (const bf16*)x, ld_x,
+                      (const bf16*)router, (const bf16*)shared_gate, width, n_experts, top, pairs, choice, in_weight, out_weight);
+    else
+        return fail("route: unknown dtype");
+    return check_launch("route_kernel");
+}
+
+extern "C" int mllm_hybrid_experts(float* hidden, long ld_hidden, void* act, long ld_act, const void* x, long ld_x,
+                                   const int* choice, const float* in_weight, const float* out_weight,
+                                   const long long* gate_of, const long long* up_of, const long long* down_of,
+                                   const int* inner_of, int max_inner, int width, int pairs, int n_tokens, int dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t shared = sizeof(float) * (size_t)width;
+    if (shared > 48 * 1024) return fail("experts: the token does not fit shared memory");
+    dim3 up_grid(n_tokens * pairs, (max_inner + UP_FEATURES - 1) / UP_FEATURES);
+    if (up_grid.y > 65535) return fail("experts: the inner size is too large for one launch");
+    int down_y = (width + 7) / 8;
+    if (down_y > 16) down_y = 16;
+    dim3 down_grid(n_tokens, down_y);
+    if (dtype == DT_F32) {
+        launch_kernel(g_dependent_launch != 0, expert_up_kernel<float>, up_grid, dim3(256), shared, s, (float*)act, ld_act,
+                      (const float*)x, ld_x, choice, in_weight, gate_of, up_of, inner_of, width, pairs);
+        launch_kernel(g_dependent_launch != 0, expert_down_kernel<float>, down_grid, dim3(256), 0, s, hidden, ld_hidden,
+                      (const float*)act, ld_act, choice, out_weight, down_of, inner_of, width, pairs);
+    } else if (dtype == DT_BF16) {
+        launch_kernel(g_dependent_launch != 0, expert_up_kernel<bf16>, up_grid, dim3(256), shared, s, (bf16*)act, ld_act,
+                      (const bf16*)x, ld_x, choice, in_weight, gate_of, up_of, inner_of, width, pairs);
+        launch_kernel(g_dependent_launch != 0, expert_down_kernel<bf16>, down_grid, dim3(256), 0, s, hidden, ld_hidden,
+                      (const bf16*)act, ld_act, choice, out_weight, down_of, inner_of, width, pairs);
+    } else {
+        return fail("experts: unknown dtype");
+    }
+    return check_launch("expert kernels");
+}
+
+// ---------------------------------------------------------------------------
+// x[r, c] += a * u[r, c] + b * v[r, c]  (32-bit; v may be null)
+// ---------------------------------------------------------------------------
+__global__ void scaled_add_kernel(float* __restrict__ x, const float* __restrict__ u, float a, const float* __restrict__ v,
+                                  float b, long n) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        float sum = a * u[i];
+        if (v != nullptr) sum = fmaf(b, v[i], sum);
+        x[i] += sum;
+    }
+}
+
+extern "C" int mllm_hybrid_scaled_add(float* x, const float* u, float a, const float* v, float b, long n, void* stream) {
+    if (n <= 0) return 0;
+    long blocks = (n + 255) / 256;
+    if (blocks > 4096) blocks = 4096;
+    launch_kernel(g_dependent_launch != 0, scaled_add_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, x, u, a, v, b, n);
+    return check_launch("scaled_add_kernel");
+}

@@ -29,10 +29,12 @@ __device__ __forceinline__ float log_sigmoid_f(float z) {
 // consecutive pieces; each is divided by sqrt(mean(piece^2) + eps); the whole is multiplied
 // by the gain.  One block per (row, group).
 //   ADD   out (fp32) += result            (a sublayer's result onto the residual stream)
-//   GATE  result *= sigmoid(gate[r, c])   (gate has the activations' element type)
+//   GATE  1: result *= sigmoid(gate[r, c]); 2: result *= silu(gate[r, c]); 3: the INPUT is
+//         multiplied by silu(gate[r, c]) before the root mean square is taken
+//         (gate has the activations' element type)
 // `rows` (may be null) gathers input rows.  out may be x itself.
 // ---------------------------------------------------------------------------
-template <typename O, typename G, bool ADD, bool GATE>
+template <typename O, typename G, bool ADD, int GATE>
 __global__ void grouped_rms_norm_kernel(O* __restrict__ out, long ld_out, const float* x, long ld_x,
                                         const float* __restrict__ gain, const int* __restrict__ rows,
                                         const G* __restrict__ gate, long ld_gate, int size, float eps) {
@@ -42,12 +44,19 @@ __global__ void grouped_rms_norm_kernel(O* __restrict__ out, long ld_out, const 
     const int r = blockIdx.x, g = blockIdx.y;
     const float* part = x + (long)(rows ? rows[r] : r) * ld_x + (long)g * size;
     float sq = 0.0f;
-    for (int d = threadIdx.x; d < size; d += blockDim.x) sq = fmaf(part[d], part[d], sq);
+    for (int d = threadIdx.x; d < size; d += blockDim.x) {
+        float v = part[d];
+        if (GATE == 3) v *= silu_f(to_f32(gate[(long)r * ld_gate + g * size + d]));
+        sq = fmaf(v, v, sq);
+    }
     const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)size + eps);
     for (int d = threadIdx.x; d < size; d += blockDim.x) {
         const int c = g * size + d;
-        float v = part[d] * inv * gain[c];
-        if (GATE) v *= sigmoid_f(to_f32(gate[(long)r * ld_gate + c]));
+        float v = part[d];
+        if (GATE == 3) v *= silu_f(to_f32(gate[(long)r * ld_gate + c]));
+        v = v * inv * gain[c];
+        if (GATE == 1) v *= sigmoid_f(to_f32(gate[(long)r * ld_gate + c]));
+        if (GATE == 2) v *= silu_f(to_f32(gate[(long)r * ld_gate + c]));
         O* o = out + (long)r * ld_out + c;
         if (ADD) *o = from_f32<O>(to_f32(*o) + v);
         else *o = from_f32<O>(v);
@@ -57,49 +66,59 @@ __global__ void grouped_rms_norm_kernel(O* __restrict__ out, long ld_out, const 
 template <typename O, typename G>
 static void launch_grouped_rms_norm(void* out, long ld_out, const float* x, long ld_x, const float* gain, const int* rows,
                                     const void* gate, long ld_gate, int n_rows, int size, int groups, float eps, int add,
-                                    cudaStream_t s) {
+                                    int gate_mode, cudaStream_t s) {
     const int threads = size >= 1024 ? 256 : (size >= 256 ? 128 : (size >= 64 ? 64 : 32));
     dim3 grid(n_rows, groups);
     O* o = (O*)out;
     const G* g = (const G*)gate;
-    if (add) launch_kernel(g_dependent_launch != 0, grouped_rms_norm_kernel<O, G, true, false>, dim3(grid), dim3(threads), 0, s, o, ld_out, x, ld_x, gain, rows, g, ld_gate, size, eps);
-    else if (gate != nullptr) launch_kernel(g_dependent_launch != 0, grouped_rms_norm_kernel<O, G, false, true>, dim3(grid), dim3(threads), 0, s, o, ld_out, x, ld_x, gain, rows, g, ld_gate, size, eps);
-    else launch_kernel(g_dependent_launch != 0, grouped_rms_norm_kernel<O, G, false, false>, dim3(grid), dim3(threads), 0, s, o, ld_out, x, ld_x, gain, rows, g, ld_gate, size, eps);
+    if (add) launch_kernel(g_dependent_launch != 0, grouped_rms_norm_kernel<O, G, true, 0>, dim3(grid), dim3(threads), 0, s, o, ld_out, x, ld_x, gain, rows, g, ld_gate, size, eps);
+    else if (gate != nullptr && gate_mode == 3) launch_kernel(g_dependent_launch != 0, grouped_rms_norm_kernel<O, G, false, 3>, dim3(grid), dim3(threads), 0, s, o, ld_out, x, ld_x, gain, rows, g, ld_gate, size, eps);
+    else if (gate != nullptr && gate_mode == 2) launch_kernel(g_dependent_launch != 0, grouped_rms_norm_kernel<O, G, false, 2>, dim3(grid), dim3(threads), 0, s, o, ld_out, x, ld_x, gain, rows, g, ld_gate, size, eps);
+    else if (gate != nullptr) launch_kernel(g_dependent_launch != 0, grouped_rms_norm_kernel<O, G, false, 1>, dim3(grid), dim3(threads), 0, s, o, ld_out, x, ld_x, gain, rows, g, ld_gate, size, eps);
+    else launch_kernel(g_dependent_launch != 0, grouped_rms_norm_kernel<O, G, false, 0>, dim3(grid), dim3(threads), 0, s, o, ld_out, x, ld_x, gain, rows, g, ld_gate, size, eps);
 }
 
 // out_dtype / gate_dtype: element types of out and gate.  add != 0: out is fp32 and is added to.
+// gate_mode: how the gate enters (1 sigmoid, 2 silu, 3 silu on the input, before the norm).
 extern "C" int mllm_sequence_grouped_rms_norm(void* out, long ld_out, const float* x, long ld_x, const float* gain,
                                               const int* rows, const void* gate, long ld_gate, int n_rows, int width,
-                                              int groups, float eps, int add, int out_dtype, int gate_dtype, void* stream) {
+                                              int groups, float eps, int add, int out_dtype, int gate_dtype, int gate_mode,
+                                              void* stream) {
     if (n_rows <= 0) return 0;
     if (groups <= 0 || width <= 0 || width % groups != 0) return fail("grouped_rms_norm: the width is not a multiple of the groups");
     if (groups > 65535) return fail("grouped_rms_norm: too many groups for one launch");
     if (add && (out_dtype != DT_F32 || gate != nullptr)) return fail("grouped_rms_norm: the residual sum is 32-bit and takes no gate");
+    if (gate != nullptr && (gate_mode < 1 || gate_mode > 3)) return fail("grouped_rms_norm: unknown gate mode");
     cudaStream_t s = (cudaStream_t)stream;
     const int size = width / groups;
     if (out_dtype == DT_F32 && (gate == nullptr || gate_dtype == DT_F32))
-        launch_grouped_rms_norm<float, float>(out, ld_out, x, ld_x, gain, rows, gate, ld_gate, n_rows, size, groups, eps, add, s);
+        launch_grouped_rms_norm<float, float>(out, ld_out, x, ld_x, gain, rows, gate, ld_gate, n_rows, size, groups, eps, add, gate_mode, s);
     else if (out_dtype == DT_BF16 && (gate == nullptr || gate_dtype == DT_BF16))
-        launch_grouped_rms_norm<bf16, bf16>(out, ld_out, x, ld_x, gain, rows, gate, ld_gate, n_rows, size, groups, eps, add, s);
+        launch_grouped_rms_norm<bf16, bf16>(out, ld_out, x, ld_x, gain, rows, gate, ld_gate, n_rows, size, groups, eps, add, gate_mode, s);
     else if (out_dtype == DT_F32 && gate_dtype == DT_BF16)
-        launch_grouped_rms_norm<float, bf16>(out, ld_out, x, ld_x, gain, rows, gate, ld_gate, n_rows, size, groups, eps, add, s);
+        launch_grouped_rms_norm<float, bf16>(out, ld_out, x, ld_x, gain, rows, gate, ld_gate, n_rows, size, groups, eps, add, gate_mode, s);
     else
         return fail("grouped_rms_norm: unsupported combination of element types");
     return check_launch("grouped_rms_norm_kernel");
 }
 
 // ---------------------------------------------------------------------------
-// Short causal convolution over time, per channel, added onto its input:
-//   out[t, c] = h[t, c] + sum_{j < taps} w[c, j] * h[t - (taps - 1) + j, c]
+// Short causal convolution over time, per channel:
+//   out[t, c] = act(identity * h[t, c] + bias[c] + sum_{j < taps} w[c, j] * h[t - (taps - 1) + j, c])
 // over the tokens of one request; inputs before this step's portion come from the request's
-// state (the last taps - 1 inputs, oldest first, zero before the sequence's start).
+// state (the last taps - 1 inputs, oldest first, zero before the sequence's start).  `identity`
+// (0 or 1) says whether the convolution is added onto its input; `bias` may be null; act is silu
+// if `silu` is set.  h and out may have row strides of their own (columns of a wider buffer),
+// and out may be h: a block reads its token's earlier rows, so a second buffer is needed only
+// when a step brings more than one token of a request (the launcher's caller sees to that).
 // One block per token.  A second kernel (one block per entry) then moves the state on.
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void causal_taps_kernel(T* __restrict__ out, const T* __restrict__ h, const float* __restrict__ w,
+__global__ void causal_taps_kernel(T* __restrict__ out, long ld_out, const T* __restrict__ h, long ld_h,
+                                   const float* __restrict__ w, const float* __restrict__ bias,
                                    const float* __restrict__ state, long state_stride, const int* __restrict__ positions,
                                    const int* __restrict__ token_item, const int* __restrict__ item_slot,
-                                   const int* __restrict__ item_start, int width, int taps) {
+                                   const int* __restrict__ item_start, int width, int taps, int identity, int silu) {
     dependents_may_start();
     wait_for_earlier_kernels();
     const int t = blockIdx.x;
@@ -107,21 +126,23 @@ __global__ void causal_taps_kernel(T* __restrict__ out, const T* __restrict__ h,
     const int local = positions[t] - item_start[item];          // tokens of this request before t in this step
     const float* held = state + (long)item_slot[item] * state_stride;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        const float mine = to_f32(h[(long)t * width + c]);
-        float acc = mine;
+        const float mine = to_f32(h[(long)t * ld_h + c]);
+        float acc = identity ? mine : 0.0f;
+        if (bias != nullptr) acc += bias[c];
         for (int back = taps - 1; back >= 1; back--) {
             float v;
-            if (local - back >= 0) v = to_f32(h[(long)(t - back) * width + c]);
+            if (local - back >= 0) v = to_f32(h[(long)(t - back) * ld_h + c]);
             else v = held[(long)(taps - 1 + local - back) * width + c];
             acc = fmaf(w[(long)c * taps + (taps - 1 - back)], v, acc);
         }
         acc = fmaf(w[(long)c * taps + taps - 1], mine, acc);
-        out[(long)t * width + c] = from_f32<T>(acc);
+        if (silu) acc = silu_f(acc);
+        out[(long)t * ld_out + c] = from_f32<T>(acc);
     }
 }
 
 template <typename T>
-__global__ void causal_taps_state_kernel(float* __restrict__ state, long state_stride, const T* __restrict__ h,
+__global__ void causal_taps_state_kernel(float* __restrict__ state, long state_stride, const T* __restrict__ h, long ld_h,
                                          const int* __restrict__ item_slot, const int* __restrict__ item_offset,
                                          const int* __restrict__ item_count, int width, int taps) {
     dependents_may_start();
@@ -135,7 +156,7 @@ __global__ void causal_taps_state_kernel(float* __restrict__ state, long state_s
         // ascending: entry s takes what lay at s + count, which no earlier write has touched
         for (int s = 0; s < taps - 1; s++) {
             const int from = count - (taps - 1) + s;             // index among this step's tokens
-            held[(long)s * width + c] = from >= 0 ? to_f32(h[(first + from) * width + c])
+            held[(long)s * width + c] = from >= 0 ? to_f32(h[(first + from) * ld_h + c])
                                                   : held[(long)(s + count) * width + c];
         }
     }
@@ -197,26 +218,31 @@ extern "C" int mllm_sequence_norm_taps_step(void* out, const float* x, const flo
     return check_launch("norm_taps_step_kernel");
 }
 
-extern "C" int mllm_sequence_causal_taps(void* out, const void* h, const float* w, float* state, long state_stride,
-                                         const int* positions, const int* token_item, const int* item_slot,
-                                         const int* item_start, const int* item_offset, const int* item_count,
-                                         int n_tokens, int n_items, int width, int taps, int writes, int dtype, void* stream) {
+// (Not in place: the state's move reads the step's inputs after the filter has run.)
+extern "C" int mllm_sequence_causal_taps(void* out, long ld_out, const void* h, long ld_h, const float* w, const float* bias,
+                                         float* state, long state_stride, const int* positions, const int* token_item,
+                                         const int* item_slot, const int* item_start, const int* item_offset,
+                                         const int* item_count, int n_tokens, int n_items, int width, int taps, int writes,
+                                         int identity, int silu, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
     if (taps < 1) return fail("causal_taps: at least one tap");
+    if (out == h && taps > 1) return fail("causal_taps: the filter does not run in place");
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = width >= 256 ? 256 : 64;
     if (dtype == DT_F32) {
-        launch_kernel(g_dependent_launch != 0, causal_taps_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (float*)out, (const float*)h, w, state, state_stride, positions,
-                                                               token_item, item_slot, item_start, width, taps);
+        launch_kernel(g_dependent_launch != 0, causal_taps_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (float*)out, ld_out,
+                      (const float*)h, ld_h, w, bias, state, state_stride, positions, token_item, item_slot, item_start, width,
+                      taps, identity, silu);
         if (writes && taps > 1)
-            launch_kernel(g_dependent_launch != 0, causal_taps_state_kernel<float>, dim3(n_items), dim3(threads), 0, s, state, state_stride, (const float*)h, item_slot,
-                                                                        item_offset, item_count, width, taps);
+            launch_kernel(g_dependent_launch != 0, causal_taps_state_kernel<float>, dim3(n_items), dim3(threads), 0, s, state,
+                          state_stride, (const float*)h, ld_h, item_slot, item_offset, item_count, width, taps);
     } else if (dtype == DT_BF16) {
-        launch_kernel(g_dependent_launch != 0, causal_taps_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, (bf16*)out, (const bf16*)h, w, state, state_stride, positions,
-                                                              token_item, item_slot, item_start, width, taps);
+        launch_kernel(g_dependent_launch != 0, causal_taps_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, (bf16*)out, ld_out,
+                      (const bf16*)h, ld_h, w, bias, state, state_stride, positions, token_item, item_slot, item_start, width,
+                      taps, identity, silu);
         if (writes && taps > 1)
-            launch_kernel(g_dependent_launch != 0, causal_taps_state_kernel<bf16>, dim3(n_items), dim3(threads), 0, s, state, state_stride, (const bf16*)h, item_slot,
-                                                                       item_offset, item_count, width, taps);
+            launch_kernel(g_dependent_launch != 0, causal_taps_state_kernel<bf16>, dim3(n_items), dim3(threads), 0, s, state,
+                          state_stride, (const bf16*)h, ld_h, item_slot, item_offset, item_count, width, taps);
     } else {
         return fail("causal_taps: unknown dtype");
     }

@@ -63,11 +63,18 @@ class Model:
             if entry.cache_of is not None:
                 needs.append(None)
                 continue
-            mine = {role: parts[role].cache_need() for role in arrangement.cache_roles(parts)}
+            mine = {}
+            for role in arrangement.cache_roles(parts):
+                need = parts[role].cache_need()
+                if isinstance(need, dict):
+                    # a part that keeps several things (its own parts' needs, by name)
+                    mine.update({f"{role}.{name}": one for name, one in need.items()})
+                else:
+                    mine[role] = need
             mine = {role: need for role, need in mine.items() if not isinstance(need, NoCache)}
             if not mine:
                 needs.append(None)
-            elif tuple(arrangement.cache_roles(parts)) == (arrangement.mixer_role(),):
+            elif tuple(mine) == (arrangement.mixer_role(),) and tuple(arrangement.cache_roles(parts)) == tuple(mine):
                 needs.append(mine[arrangement.mixer_role()])
             else:
                 needs.append(mine)

@@ -42,6 +42,7 @@ LIBRARIES = {
     "attention": "attention_tcgen05.cu",
     "fused": "fused_decode.cu",
     "sequence": "sequence_kernels.cu",
+    "hybrid": "hybrid_kernels.cu",
 }
 
 _lock = threading.Lock()

@@ -92,13 +92,15 @@ class Kernels:
         return ops.layernorm(out, x, gamma, beta, eps, rows)
 
     # ---- norms in groups, short convolutions, latent attention, matrix memories, layer results ----
-    def grouped_rms_norm(self, out, x, gain, groups, eps, rows=None, gate=None, add=False):
+    def grouped_rms_norm(self, out, x, gain, groups, eps, rows=None, gate=None, add=False, gate_mode="sigmoid"):
         self.launches += 1
-        return ops.grouped_rms_norm(out, x, gain, groups, eps, rows, gate, add)
+        return ops.grouped_rms_norm(out, x, gain, groups, eps, rows, gate, add, gate_mode)
 
-    def causal_taps(self, ctx, out, h, w, state, writes=True):
+    def causal_taps(self, ctx, out, h, w, state, writes=True, identity=True, bias=None, silu=False):
+        plain_filter = identity and bias is None and not silu
         if isinstance(h, DeferredNorm):
-            if h.kind == "grouped_rms_norm" and h.rows is None and ctx.decode_only and w.shape[1] > 1:
+            if (plain_filter and h.kind == "grouped_rms_norm" and h.rows is None and ctx.decode_only
+                    and w.shape[1] > 1):
                 # single tokens: norm, filter and the state's move in one kernel
                 self.launches += 1
                 self.chose("causal_taps", "norm_taps_step", out.shape[0], out.shape[1], w.shape[1])
@@ -107,7 +109,42 @@ class Kernels:
         self.chose("causal_taps", "causal_taps", out.shape[0], out.shape[1], w.shape[1])
         self.launches += 2 if writes and w.shape[1] > 1 else 1
         return ops.causal_taps(out, h, w, state, ctx.positions, ctx.token_item, ctx.item_slot, ctx.item_start,
-                               ctx.item_offset, ctx.item_count, writes)
+                               ctx.item_offset, ctx.item_count, writes, identity, bias, silu)
+
+    # ---- rotary positions with the cache store, capped attention, linear recurrences, routed experts ----
+    def rotary_store(self, ctx, cache, qkv, k_off, v_off, heads, kv_heads, dim, vdim, rot_dims, inv_freq, amplitude):
+        self.launches += 1
+        return ops.rotary_store(qkv, k_off, v_off, heads, kv_heads, dim, vdim, rot_dims, inv_freq, amplitude, ctx.positions,
+                                ctx.token_item, cache.block_table, cache.page_size, cache.k_pages, cache.v_pages, cache.writes)
+
+    def capped_attention(self, ctx, out, q, cache, n_heads, n_kv_heads, dim, vdim, scale, cap=0.0, window=0):
+        """Attention whose weights stay 32-bit, with a cap on the scores and values of a size of
+        their own.  Steps with prompt portions take the tiles (tokens of a request side by side
+        share the cached rows they read); steps of single tokens, and sizes the tiles do not take,
+        one block per (token, head)."""
+        self.launches += 1
+        tiled = not ctx.decode_only and ops.capped_attention_tiled_takes(dim, vdim)
+        self.chose("capped_attention", "capped_attention_tiled" if tiled else "capped_attention_plain", q.shape[0], n_heads, dim, vdim)
+        return ops.capped_attention(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions, ctx.token_item,
+                                    n_heads, n_kv_heads, dim, vdim, cache.page_size, scale, cap, window, tiled)
+
+    def linear_recurrence(self, ctx, out, q, k, v, gate_a, gate_b, log_rate, step_bias, state, heads, qk_heads, dim, vdim,
+                          delta, unit_norm=False, q_scale=1.0, skip=None, writes=True):
+        self.launches += 1
+        return ops.linear_recurrence(out, q, k, v, gate_a, gate_b, log_rate, step_bias, state, ctx.item_slot, ctx.item_offset,
+                                     ctx.item_count, heads, qk_heads, dim, vdim, delta, unit_norm, q_scale, skip, writes)
+
+    def route(self, x, router, shared_gate, top, choice, in_weight, out_weight):
+        self.launches += 1
+        return ops.route(x, router, shared_gate, top, choice, in_weight, out_weight)
+
+    def experts(self, hidden, act, x, choice, in_weight, out_weight, gate_of, up_of, down_of, inner_of, max_inner, pairs):
+        self.launches += 2
+        return ops.experts(hidden, act, x, choice, in_weight, out_weight, gate_of, up_of, down_of, inner_of, max_inner, pairs)
+
+    def scaled_add(self, x, u, a, v=None, b=0.0):
+        self.launches += 1
+        return ops.scaled_add(x, u, a, v, b)
 
     def latent_prepare(self, ctx, cache, q_eff, down, q, gain, inv_freq, rank, rot, rot_dims, heads, dim, eps):
         self.launches += 1

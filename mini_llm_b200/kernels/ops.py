@@ -785,14 +785,17 @@ def device_info() -> dict:
 # ---- norms in groups, short convolutions, latent attention, matrix memories ----------------------
 
 _grouped_rms_norm = Function("sequence", "mllm_sequence_grouped_rms_norm",
-                             [P, L, P, L, P, P, P, L, I, I, I, F, I, I, I, P])
+                             [P, L, P, L, P, P, P, L, I, I, I, F, I, I, I, I, P])
+
+GATE_MODES = {"sigmoid": 1, "silu": 2, "silu_before": 3}
 
 
-def grouped_rms_norm(out, x, gain, groups, eps, rows=None, gate=None, add=False):
+def grouped_rms_norm(out, x, gain, groups, eps, rows=None, gate=None, add=False, gate_mode="sigmoid"):
     """Rows of the fp32 ``x`` [*, width], cut into ``groups`` equal consecutive pieces, each divided by
     sqrt(mean(piece^2) + eps), the whole times ``gain``.  ``rows`` gathers input rows.  ``gate``
-    [R, width]: the result is also multiplied by sigmoid(gate).  ``add``: the fp32 ``out`` is added
-    to.  ``out`` may be ``x``."""
+    [R, width]: the result is also multiplied by sigmoid(gate) (``gate_mode`` "sigmoid") or by
+    silu(gate) ("silu"); with "silu_before" the input is multiplied by silu(gate) before the norm.
+    ``add``: the fp32 ``out`` is added to.  ``out`` may be ``x``."""
     _check(out, "grouped_rms_norm.out", None, 2)
     _check(x, "grouped_rms_norm.x", torch.float32, 2)
     _check(gain, "grouped_rms_norm.gain", torch.float32, 1)
@@ -813,17 +816,22 @@ def grouped_rms_norm(out, x, gain, groups, eps, rows=None, gate=None, add=False)
         raise KernelError("grouped_rms_norm: the residual sum is kept in 32-bit and takes no gate")
     _grouped_rms_norm(out.data_ptr(), out.stride(0), x.data_ptr(), x.stride(0), gain.data_ptr(), _ptr(rows), _ptr(gate),
                       gate.stride(0) if gate is not None else 0, n_rows, width, int(groups), float(eps), int(bool(add)),
-                      dtype_code(out.dtype), dtype_code(gate.dtype) if gate is not None else 0, _stream())
+                      dtype_code(out.dtype), dtype_code(gate.dtype) if gate is not None else 0, GATE_MODES[gate_mode],
+                      _stream())
     return out
 
 
-_causal_taps = Function("sequence", "mllm_sequence_causal_taps", [P, P, P, P, L, P, P, P, P, P, P, I, I, I, I, I, I, P])
+_causal_taps = Function("sequence", "mllm_sequence_causal_taps",
+                        [P, L, P, L, P, P, P, L, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P])
 
 
-def causal_taps(out, h, w, state, positions, token_item, item_slot, item_start, item_offset, item_count, writes=True):
-    """out[t] = h[t] + sum_j w[:, j] * h[t - (taps - 1) + j] over the tokens of one request, per
+def causal_taps(out, h, w, state, positions, token_item, item_slot, item_start, item_offset, item_count, writes=True,
+                identity=True, bias=None, silu=False):
+    """out[t] = act(h[t] + bias + sum_j w[:, j] * h[t - (taps - 1) + j]) over the tokens of one request, per
     channel; what lies before this step's portion comes from ``state`` [slots, taps - 1, width]
-    (fp32, oldest first), which is then moved on by this step's tokens (unless ``writes`` is false)."""
+    (fp32, oldest first), which is then moved on by this step's tokens (unless ``writes`` is false).
+    ``identity`` false: the input itself is not added (a plain convolution); ``bias`` [width] fp32 or
+    None; ``silu``: the activation.  ``h`` and ``out`` may be column ranges of wider buffers."""
     _check(out, "causal_taps.out", h.dtype, 2)
     _check(h, "causal_taps.h", None, 2)
     _check(w, "causal_taps.w", torch.float32, 2)
@@ -833,13 +841,18 @@ def causal_taps(out, h, w, state, positions, token_item, item_slot, item_start, 
         _check(t, f"causal_taps.{name}", torch.int32, 1)
     n, width = h.shape
     taps = w.shape[1]
-    if not (out.is_contiguous() and h.is_contiguous() and w.is_contiguous()) or w.shape[0] != width or out.shape != h.shape:
-        raise KernelError("causal_taps: out, h and w must be contiguous and agree on the width")
+    if not w.is_contiguous() or w.shape[0] != width or out.shape != h.shape:
+        raise KernelError("causal_taps: out, h and w must agree on the width")
+    if bias is not None:
+        _check(bias, "causal_taps.bias", torch.float32, 1)
+        if bias.shape[0] != width:
+            raise KernelError("causal_taps: one bias per channel")
     if tuple(state.shape[1:]) != (max(taps - 1, 0), width) or (taps > 1 and state.stride(1) != width):
         raise KernelError(f"causal_taps: the state must be [slots, {taps - 1}, {width}]")
-    _causal_taps(out.data_ptr(), h.data_ptr(), w.data_ptr(), state.data_ptr(), state.stride(0), positions.data_ptr(),
-                 token_item.data_ptr(), item_slot.data_ptr(), item_start.data_ptr(), item_offset.data_ptr(),
-                 item_count.data_ptr(), n, item_count.shape[0], width, taps, int(bool(writes)), dtype_code(h.dtype), _stream())
+    _causal_taps(out.data_ptr(), out.stride(0), h.data_ptr(), h.stride(0), w.data_ptr(), _ptr(bias), state.data_ptr(),
+                 state.stride(0), positions.data_ptr(), token_item.data_ptr(), item_slot.data_ptr(), item_start.data_ptr(),
+                 item_offset.data_ptr(), item_count.data_ptr(), n, item_count.shape[0], width, taps, int(bool(writes)),
+                 int(bool(identity)), int(bool(silu)), dtype_code(h.dtype), _stream())
     return out
 
 
@@ -1130,3 +1143,181 @@ def depth_mix(hidden, kept, weights, index):
             raise KernelError(f"depth_mix: {weights.shape[0]} weights for {index + 1} results")
     _depth_mix(hidden.data_ptr(), kept.data_ptr(), _ptr(weights), index, kept.shape[1], n, width, _stream())
     return hidden
+
+
+# ---- rotary positions with a cache store, capped attention, linear recurrences, routed experts ----
+
+_rotary_store = Function("hybrid", "mllm_hybrid_rotary_store",
+                         [P, L, I, I, I, I, I, I, I, P, ctypes.c_double, P, P, P, I, I, P, P, I, I, I, P])
+
+
+def rotary_store(qkv, k_off, v_off, heads, kv_heads, dim, vdim, rot_dims, inv_freq, amplitude, positions, token_item,
+                 block_table, page_size, k_pages, v_pages, writes=True):
+    """Rows of ``qkv`` hold [q | k | v] (k from column ``k_off``, v from ``v_off``).  The first
+    ``rot_dims`` entries of every query and key head turn in interleaved pairs by
+    position * ``inv_freq`` [rot_dims / 2] (float64); cosine and sine are multiplied by ``amplitude``.
+    Queries and keys are rotated in place; keys and values go to the token's place in the pages."""
+    _check(qkv, "rotary_store.qkv", None, 2)
+    _check(inv_freq, "rotary_store.inv_freq", torch.float64, 1)
+    _check(k_pages, "rotary_store.k_pages", qkv.dtype)
+    _check(v_pages, "rotary_store.v_pages", qkv.dtype)
+    _check(block_table, "rotary_store.block_table", torch.int32, 2)
+    if inv_freq.shape[0] < max(rot_dims // 2, 1) or v_off + kv_heads * vdim > qkv.shape[1] or k_off + kv_heads * dim > qkv.shape[1]:
+        raise KernelError("rotary_store: sizes do not agree")
+    if (not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous()
+            or k_pages.numel() % (page_size * kv_heads * dim) != 0 or v_pages.numel() % (page_size * kv_heads * vdim) != 0):
+        raise KernelError("rotary_store: the pages do not hold whole pages of these rows")
+    _rotary_store(qkv.data_ptr(), qkv.stride(0), k_off, v_off, heads, kv_heads, dim, vdim, rot_dims, inv_freq.data_ptr(),
+                  float(amplitude), positions.data_ptr(), token_item.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+                  page_size, k_pages.data_ptr(), v_pages.data_ptr(), int(bool(writes)), qkv.shape[0], dtype_code(qkv.dtype),
+                  _stream())
+
+
+_capped_attention = Function("hybrid", "mllm_hybrid_capped_attention",
+                             [P, L, P, L, P, P, P, I, P, P, I, I, I, I, I, I, F, F, I, I, I, P])
+
+
+def capped_attention_tiled_takes(dim, vdim) -> bool:
+    """Whether the tiled kernel takes the sizes: a block's queries, 32 keys and 32 values lie in
+    shared memory in 32-bit (the launcher's own arithmetic)."""
+    return (0 < dim <= 256 and 0 < vdim <= 256 and dim % 4 == 0
+            and 4 * (16 * dim + 32 * (dim + 4) + 32 * vdim + 512) <= 160 * 1024)
+
+
+def capped_attention(out, q, k_pages, v_pages, block_table, positions, token_item, n_heads, n_kv_heads, dim, vdim,
+                     page_size, scale, cap=0.0, window=0, tiled=False):
+    """Causal attention of every token of the step over its request's pages, keys of ``dim`` and
+    values of ``vdim`` entries per head, score = cap * tanh(q . k * scale / cap) (``cap`` 0: no cap);
+    scores, weights and the weighted sum in 32-bit.  ``tiled``: consecutive tokens of a request share
+    the cached rows they read (for steps with prompt portions)."""
+    _check(out, "capped_attention.out", q.dtype, 2)
+    _check(q, "capped_attention.q", None, 2)
+    _check(k_pages, "capped_attention.k_pages", q.dtype)
+    _check(v_pages, "capped_attention.v_pages", q.dtype)
+    _check(block_table, "capped_attention.block_table", torch.int32, 2)
+    n = q.shape[0]
+    if q.shape[1] != n_heads * dim or out.shape != (n, n_heads * vdim):
+        raise KernelError("capped_attention: q / out do not have heads * size columns")
+    if not k_pages.is_contiguous() or not v_pages.is_contiguous() or not block_table.is_contiguous():
+        raise KernelError("capped_attention: pages and block table must be contiguous")
+    _capped_attention(out.data_ptr(), out.stride(0), q.data_ptr(), q.stride(0), k_pages.data_ptr(), v_pages.data_ptr(),
+                      block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), token_item.data_ptr(), n, n_heads,
+                      n_kv_heads, dim, vdim, page_size, float(scale), float(cap or 0.0), int(window or 0), int(bool(tiled)),
+                      dtype_code(q.dtype), _stream())
+    return out
+
+
+class _RecurrenceParams(ctypes.Structure):
+    _fields_ = [("out", P), ("ld_out", L), ("q", P), ("k", P), ("v", P), ("ld_q", L), ("ld_k", L), ("ld_v", L),
+                ("gate_a", P), ("gate_b", P), ("ld_gate_a", L), ("ld_gate_b", L), ("log_rate", P), ("step_bias", P),
+                ("skip", P), ("state", P), ("state_stride", L), ("item_slot", P), ("item_offset", P), ("item_count", P),
+                ("heads", I), ("qk_heads", I), ("dim", I), ("vdim", I), ("q_scale", F), ("delta", I), ("unit_norm", I),
+                ("writes", I)]
+
+
+_linear_recurrence = Function("hybrid", "mllm_hybrid_linear_recurrence", [ctypes.POINTER(_RecurrenceParams), I, I, P])
+
+
+def linear_recurrence(out, q, k, v, gate_a, gate_b, log_rate, step_bias, state, item_slot, item_offset, item_count, heads,
+                      qk_heads, dim, vdim, delta, unit_norm=False, q_scale=1.0, skip=None, writes=True):
+    """Per entry, its tokens in order, per head with the state S [dim, vdim] (fp32, in ``state``
+    [slots, heads * dim * vdim]): step = softplus(gate_a[t, h] + step_bias[h]), a = exp(-exp(log_rate[h]) * step);
+    without ``delta``: u = step * v; with: u = sigmoid(gate_b[t, h]) * (v - (a S)^T k); S <- a S + k u^T;
+    out[t, h] = S^T q (+ skip[h] * v).  q, k [T, qk_heads * dim] (head h reads h // (heads // qk_heads)),
+    v [T, heads * vdim], any row stride; gates fp32 [T, heads]; out fp32 [T, heads * vdim].  ``unit_norm``:
+    q and k are divided by sqrt(sum(x^2) + 1e-6) per head first; q is multiplied by ``q_scale``."""
+    _check(out, "linear_recurrence.out", torch.float32, 2)
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _check(t, f"linear_recurrence.{name}", q.dtype, 2)
+    _check(gate_a, "linear_recurrence.gate_a", torch.float32, 2)
+    _check(state, "linear_recurrence.state", torch.float32, 2)
+    for name, t in (("log_rate", log_rate), ("step_bias", step_bias)):
+        _check(t, f"linear_recurrence.{name}", torch.float32, 1)
+    n = q.shape[0]
+    if (q.shape[1] != qk_heads * dim or k.shape[1] != qk_heads * dim or v.shape[1] != heads * vdim
+            or out.shape != (n, heads * vdim) or state.shape[1] != heads * dim * vdim or state.stride(1) != 1
+            or gate_a.shape[1] < heads or log_rate.shape[0] != heads or step_bias.shape[0] != heads):
+        raise KernelError("linear_recurrence: sizes do not agree")
+    params = _RecurrenceParams()
+    params.out, params.ld_out = out.data_ptr(), out.stride(0)
+    params.q, params.k, params.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    params.ld_q, params.ld_k, params.ld_v = q.stride(0), k.stride(0), v.stride(0)
+    params.gate_a, params.ld_gate_a = gate_a.data_ptr(), gate_a.stride(0)
+    if gate_b is not None:
+        _check(gate_b, "linear_recurrence.gate_b", torch.float32, 2)
+        params.gate_b, params.ld_gate_b = gate_b.data_ptr(), gate_b.stride(0)
+    elif delta:
+        raise KernelError("linear_recurrence: the delta rule needs its write gates")
+    params.log_rate, params.step_bias = log_rate.data_ptr(), step_bias.data_ptr()
+    if skip is not None:
+        _check(skip, "linear_recurrence.skip", torch.float32, 1)
+        params.skip = skip.data_ptr()
+    params.state, params.state_stride = state.data_ptr(), state.stride(0)
+    params.item_slot, params.item_offset, params.item_count = item_slot.data_ptr(), item_offset.data_ptr(), item_count.data_ptr()
+    params.heads, params.qk_heads, params.dim, params.vdim = heads, qk_heads, dim, vdim
+    params.q_scale, params.delta, params.unit_norm, params.writes = float(q_scale), int(bool(delta)), int(bool(unit_norm)), int(bool(writes))
+    _linear_recurrence(ctypes.byref(params), item_count.shape[0], dtype_code(q.dtype), _stream())
+    return out
+
+
+_route = Function("hybrid", "mllm_hybrid_route", [P, L, P, P, I, I, I, P, P, P, I, I, P])
+_experts = Function("hybrid", "mllm_hybrid_experts", [P, L, P, L, P, L, P, P, P, P, P, P, P, I, I, I, I, I, P])
+
+
+def route(x, router, shared_gate, top, choice, in_weight, out_weight):
+    """Per row of ``x``: sigmoid scores of ``router`` [experts, width] (sums in 32-bit), the ``top``
+    largest with their scores as input weights; with ``shared_gate`` [1, width] one more pair per
+    token: expert ``experts``, input weight 1, output weight sigmoid(shared_gate . x).
+    choice int32, in_weight / out_weight fp32: [T * pairs]."""
+    _check(x, "route.x", None, 2)
+    _check(router, "route.router", x.dtype, 2)
+    _check(choice, "route.choice", torch.int32, 1)
+    _check(in_weight, "route.in_weight", torch.float32, 1)
+    _check(out_weight, "route.out_weight", torch.float32, 1)
+    n, width = x.shape
+    pairs = top + (1 if shared_gate is not None else 0)
+    if router.shape[1] != width or not router.is_contiguous() or min(choice.shape[0], in_weight.shape[0], out_weight.shape[0]) < n * pairs:
+        raise KernelError("route: sizes do not agree")
+    if shared_gate is not None:
+        _check(shared_gate, "route.shared_gate", x.dtype)
+        if shared_gate.numel() != width or not shared_gate.is_contiguous():
+            raise KernelError("route: the shared expert's gate is one row of the width")
+    _route(x.data_ptr(), x.stride(0), router.data_ptr(), _ptr(shared_gate), width, router.shape[0], top, choice.data_ptr(),
+           in_weight.data_ptr(), out_weight.data_ptr(), n, dtype_code(x.dtype), _stream())
+
+
+def experts(hidden, act, x, choice, in_weight, out_weight, gate_of, up_of, down_of, inner_of, max_inner, pairs):
+    """hidden[t] += sum over the token's ``pairs`` of out_weight * W_down[e] (silu(W_gate[e] x') * (W_up[e] x')),
+    x' = in_weight * x[t] rounded to the activations' type; expert e's matrices are named by the
+    int64 pointer tables ``gate_of``, ``up_of``, ``down_of`` and its inner size by ``inner_of`` (int32).
+    ``act`` [T * pairs, max_inner] is scratch."""
+    _check(hidden, "experts.hidden", torch.float32, 2)
+    _check(x, "experts.x", None, 2)
+    _check(act, "experts.act", x.dtype, 2)
+    for name, t in (("gate_of", gate_of), ("up_of", up_of), ("down_of", down_of)):
+        _check(t, f"experts.{name}", torch.int64, 1)
+    _check(inner_of, "experts.inner_of", torch.int32, 1)
+    n, width = x.shape
+    if hidden.shape != (n, width) or act.shape[0] < n * pairs or act.shape[1] < max_inner:
+        raise KernelError("experts: sizes do not agree")
+    _experts(hidden.data_ptr(), hidden.stride(0), act.data_ptr(), act.stride(0), x.data_ptr(), x.stride(0), choice.data_ptr(),
+             in_weight.data_ptr(), out_weight.data_ptr(), gate_of.data_ptr(), up_of.data_ptr(), down_of.data_ptr(),
+             inner_of.data_ptr(), int(max_inner), width, int(pairs), n, dtype_code(x.dtype), _stream())
+    return hidden
+
+
+_scaled_add = Function("hybrid", "mllm_hybrid_scaled_add", [P, P, F, P, F, L, P])
+
+
+def scaled_add(x, u, a, v=None, b=0.0):
+    """x += a * u + b * v (fp32, contiguous, equal shapes; ``v`` may be None)."""
+    _check(x, "scaled_add.x", torch.float32)
+    _check(u, "scaled_add.u", torch.float32)
+    if not x.is_contiguous() or not u.is_contiguous() or u.shape != x.shape:
+        raise KernelError("scaled_add: x and u must be contiguous and of one shape")
+    if v is not None:
+        _check(v, "scaled_add.v", torch.float32)
+        if not v.is_contiguous() or v.shape != x.shape:
+            raise KernelError("scaled_add: v must be contiguous and of x's shape")
+    _scaled_add(x.data_ptr(), u.data_ptr(), float(a), _ptr(v), float(b), x.numel(), _stream())
+    return x

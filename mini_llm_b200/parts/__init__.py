@@ -1,7 +1,8 @@
 """Parts a model is put together from.  Importing the package registers the
 built-in kinds; ``register_part`` / ``register_arrangement`` add others."""
 
-from . import attention, block, depth, embedding, filter, latent_attention, matrix_memory, mlp, norm  # noqa: F401  (register themselves)
+from . import (attention, block, depth, embedding, experts, filter, latent_attention, matrix_memory, mlp, norm,  # noqa
+               recurrence, rotary)  # noqa: F401  (register themselves)
 from .base import (Arrangement, Embedding, FeedForward, Head, InputFilter, Mixer, Norm, Part, PositionEncoding,
                    build_part, get_arrangement, register_arrangement, register_part)
 from .spec import (FixedState, LayerSpec, ModelSpec, NoCache, PagedKV, PartSpec, RunEntry, WeightSpec)

@@ -25,8 +25,10 @@ fused projection, which scatters straight into the pages, knows no rotation).
 
 from __future__ import annotations
 
+import torch
+
 from .base import Mixer, build_part, register_part
-from .spec import PagedKV, WeightSpec
+from .spec import FixedState, PagedKV, WeightSpec
 
 
 class CausalSelfAttention(Mixer):
@@ -105,4 +107,93 @@ class CausalSelfAttention(Mixer):
                  epilogue="add")
 
 
+class FilteredAttention(Mixer):
+    """Causal attention whose queries, keys and values pass a short causal convolution over time
+    before rotary positions, with a tanh cap on the scores and values of a size of their own.
+
+    ``q = W_q x + b_q`` and likewise k, v (one product over the stacked matrices); every channel of
+    q, k and v is then filtered, ``y_t = sum_j w[:, j] u_(t - taps + 1 + j)`` (no bias, zeros before
+    the sequence's start; the last ``taps - 1`` projected rows of a request are its state); the
+    position encoding (``position``: a part with ``rotate_store``) turns q and k and the keys and
+    values go to the pages; ``score = cap * tanh(q . k * scale / cap)`` over the keys at positions
+    <= the query's (or the last ``window``), softmax and the weighted sum in 32-bit; query head h
+    reads key/value head ``h // (heads / kv_heads)``; then ``W_o`` with its bias.  ``compute`` returns
+    the output itself in 32-bit; ``forward`` adds it onto the stream."""
+
+    graph_safe = True
+
+    def __init__(self, prefix, width: int, n_heads: int, n_kv_heads: int, key_size: int, value_size: int,
+                 score_scale: float, taps: int, position, softcap: float | None = None, window: int | None = None,
+                 names: dict | None = None):
+        super().__init__(prefix)
+        self.width, self.n_heads, self.n_kv_heads = int(width), int(n_heads), int(n_kv_heads)
+        self.dim, self.vdim, self.taps = int(key_size), int(value_size), int(taps)
+        self.score_scale = float(score_scale)
+        self.softcap = float(softcap) if softcap else 0.0
+        self.window = int(window) if window else None
+        if min(self.n_heads, self.n_kv_heads, self.dim, self.vdim) <= 0 or self.n_heads % self.n_kv_heads != 0:
+            raise ValueError(f"{prefix}: {self.n_heads} heads are not a positive multiple of {self.n_kv_heads} key/value heads")
+        if self.taps < 1:
+            raise ValueError(f"{prefix}: a convolution has at least one tap")
+        self.position = build_part(position)
+        if not hasattr(self.position, "rotate_store"):
+            raise ValueError(f"{prefix}: the position encoding '{position.kind}' has no rotate_store(ctx, cache, qkv, ...)")
+        self.names = dict(q="q", k="k", v="v", o="o", bias=".b", taps=".conv")
+        self.names.update(names or {})
+        self.q_width, self.k_width, self.v_width = self.n_heads * self.dim, self.n_kv_heads * self.dim, self.n_kv_heads * self.vdim
+        self.qkv_width = self.q_width + self.k_width + self.v_width
+
+    def weight_specs(self):
+        n = self.names
+        specs = list(self.position.weight_specs())
+        for name, rows in ((n["q"], self.q_width), (n["k"], self.k_width), (n["v"], self.v_width)):
+            specs += [WeightSpec(self.full_name(name), (rows, self.width)),
+                      WeightSpec(self.full_name(name + n["bias"]), (rows,), role="vector", init="bias"),
+                      WeightSpec(self.full_name(name + n["taps"]), (rows, self.taps), role="vector", init="matrix")]
+        specs += [WeightSpec(self.full_name(n["o"]), (self.width, self.n_heads * self.vdim), init="residual_matrix"),
+                  WeightSpec(self.full_name(n["o"] + n["bias"]), (self.width,), role="vector", init="bias")]
+        return specs
+
+    def cache_need(self):
+        need = {"kv": PagedKV(self.n_kv_heads, self.dim, self.window, value_size=self.vdim)}
+        if self.taps > 1:
+            need["taps"] = FixedState((self.taps - 1, self.qkv_width), "float32")
+        return need
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        n = self.names
+        self.position.bind({w.name: tensors[w.name] for w in self.position.weight_specs() if w.name in tensors}, runtime)
+        three = (n["q"], n["k"], n["v"])
+        self.stacked = torch.cat([self.w(name) for name in three]).contiguous()
+        self.stacked_bias = torch.cat([self.w(name + n["bias"]) for name in three]).contiguous()
+        self.stacked_taps = torch.cat([self.w(name + n["taps"]) for name in three]).contiguous()
+        self._no_state = torch.zeros((1, 0, self.qkv_width), dtype=torch.float32, device=self.stacked.device)
+
+    def compute(self, ctx, x, cache):
+        k, n = ctx.kernels, x.shape[0]
+        pages = cache.of("kv")
+        projected = ctx.buffer("qkv", (n, self.qkv_width), ctx.act_dtype)
+        k.linear(ctx, projected, x, self.stacked, self.stacked_bias)
+        if self.taps > 1:
+            held = cache.of("taps")
+            qkv = ctx.buffer("qkv_filtered", (n, self.qkv_width), ctx.act_dtype)
+            k.causal_taps(ctx, qkv, projected, self.stacked_taps, held.state, held.writes, identity=False)
+        else:
+            qkv = ctx.buffer("qkv_filtered", (n, self.qkv_width), ctx.act_dtype)
+            k.causal_taps(ctx, qkv, projected, self.stacked_taps, self._no_state, False, identity=False)
+        self.position.rotate_store(ctx, pages, qkv, self.q_width, self.q_width + self.k_width, self.n_heads, self.n_kv_heads,
+                                   self.dim, self.vdim)
+        mixed = ctx.buffer("attn_out", (n, self.n_heads * self.vdim), ctx.act_dtype)
+        k.capped_attention(ctx, mixed, qkv[:, :self.q_width], pages, self.n_heads, self.n_kv_heads, self.dim, self.vdim,
+                           self.score_scale, self.softcap, self.window or 0)
+        out = ctx.buffer("mixer_out", (n, self.width), torch.float32)
+        k.linear(ctx, out, mixed, self.w(self.names["o"]), self.w(self.names["o"] + self.names["bias"]))
+        return out
+
+    def forward(self, ctx, x, hidden, cache):
+        ctx.kernels.scaled_add(hidden, self.compute(ctx, x, cache), 1.0)
+
+
 register_part("causal_self_attention", CausalSelfAttention)
+register_part("filtered_attention", FilteredAttention)

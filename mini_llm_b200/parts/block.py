@@ -24,15 +24,19 @@ def _defer(norm, consumer) -> dict:
 
 
 class PreNorm(Arrangement):
-    roles = ("norm_1", "mixer", "norm_2", "feed_forward")
+    roles = ("norm_1", "mixer")
+    optional_roles = ("norm_2", "feed_forward")      # a layer may have no feed-forward
 
     def run(self, ctx, parts, hidden, cache):
         # A part that states ``accepts_deferred_norm`` may get its input norm unevaluated
         # (to fuse it into its first product); any other part gets a tensor.
         x = parts["norm_1"].forward(ctx, hidden, tag="norm_1", **_defer(parts["norm_1"], parts["mixer"]))
+        if getattr(cache, "kind", "none") == "composite":
+            cache = cache.sub("mixer")               # a mixer that keeps several things gets them by its own names
         parts["mixer"].forward(ctx, x, hidden, cache)
-        x = parts["norm_2"].forward(ctx, hidden, tag="norm_2", **_defer(parts["norm_2"], parts["feed_forward"]))
-        parts["feed_forward"].forward(ctx, x, hidden)
+        if "feed_forward" in parts:
+            x = parts["norm_2"].forward(ctx, hidden, tag="norm_2", **_defer(parts["norm_2"], parts["feed_forward"]))
+            parts["feed_forward"].forward(ctx, x, hidden)
 
 
 class SandwichNorm(Arrangement):

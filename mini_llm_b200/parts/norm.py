@@ -6,7 +6,8 @@ Norm by root mean square in groups (``grouped_rms_norm``): the row is cut into `
 consecutive pieces, each divided by ``sqrt(mean(piece^2) + eps)``, and the whole multiplied by one
 gain vector; ``groups=1`` is the plain RMS norm.  Besides the interface of every norm it can norm
 the residual stream in place and add a normed sublayer result onto it, which is what an
-arrangement with norms on both sides of a sublayer needs."""
+arrangement with norms on both sides of a sublayer needs.  With ``unit_offset`` the stored weight lies
+around zero and the gain is ``1 + weight`` (added once, in 32-bit, when the weights arrive)."""
 
 from __future__ import annotations
 
@@ -46,14 +47,21 @@ class GroupedRmsNorm(Norm):
     graph_safe = True
     can_defer = True
 
-    def __init__(self, prefix, width: int, eps: float, groups: int = 1, name: str = "weight"):
+    def __init__(self, prefix, width: int, eps: float, groups: int = 1, name: str = "weight", unit_offset: bool = False):
         super().__init__(prefix)
         self.width, self.eps, self.groups, self.name = int(width), float(eps), int(groups), name
+        self.unit_offset = bool(unit_offset)
         if self.groups <= 0 or self.width % self.groups != 0:
             raise ValueError(f"{self.full_name(name)}: a width of {self.width} does not split into {self.groups} equal groups")
 
     def weight_specs(self):
-        return [WeightSpec(self.full_name(self.name), (self.width,), role="vector", init="gain")]
+        return [WeightSpec(self.full_name(self.name), (self.width,), role="vector", init="shift" if self.unit_offset else "gain")]
+
+    def bind(self, tensors, runtime):
+        if self.unit_offset:
+            name = self.full_name(self.name)
+            tensors = {**tensors, name: tensors[name] + 1.0}
+        super().bind(tensors, runtime)
 
     def forward(self, ctx, x, rows=None, tag="norm", defer=False):
         if defer:

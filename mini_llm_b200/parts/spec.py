@@ -109,12 +109,14 @@ class ModelSpec:
 class PagedKV:
     """Keys and values of every cached token (or of the last ``window`` tokens), in pages.
     With ``has_values`` false only one row per token is kept (the ``keys``): a mixer whose values
-    are a part of that row (attention over a shared latent) needs no second pool."""
+    are a part of that row (attention over a shared latent) needs no second pool.  ``value_size``:
+    the size of a value per head where it differs from the keys' ``head_size``."""
 
     n_kv_heads: int
     head_size: int
     window: int | None = None          # None: all keys
     has_values: bool = True
+    value_size: int | None = None      # None: as head_size
 
 
 @dataclass(frozen=True)
