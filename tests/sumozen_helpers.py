@@ -48,10 +48,19 @@ def full_stack(**kw):
                   **kw)
 
 
-def make_model(folder, raw, seed=0, bend=None, matrix_scale=1.0):
+def to_bfloat16_values(values):
+    """The nearest values that bfloat16 holds (ties to even), still as float32."""
+    bits = np.ascontiguousarray(values, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    bits = (bits + 0x7FFF + ((bits >> 16) & 1)) & 0xFFFF0000
+    return bits.astype(np.uint32).view(np.float32).reshape(np.shape(values))
+
+
+def make_model(folder, raw, seed=0, bend=None, matrix_scale=1.0, bfloat16_values=False):
     """Write config.json and model.safetensors (32-bit) with random weights: matrices N(0, 0.05)
     times ``matrix_scale``, gains U(0.5, 1.5), norm offsets N(0, 0.1), biases N(0, 0.02).
-    ``bend(tensors)`` may change them before they are written."""
+    ``bend(tensors)`` may change them before they are written.  ``bfloat16_values``: every value is
+    one that bfloat16 holds, as in a model that was stored in that type, so that a bfloat16
+    engine and the plain model compute with the same weights."""
     parsed = config_from_dict(raw)
     tensors = random_tensors(describe_model(parsed), seed, "varied")
     for name, values in tensors.items():
@@ -61,6 +70,8 @@ def make_model(folder, raw, seed=0, bend=None, matrix_scale=1.0):
             values *= 8.0                   # taps of about 0.4: every tap matters
     if bend is not None:
         bend(tensors)
+    if bfloat16_values:
+        tensors = {name: to_bfloat16_values(values) for name, values in tensors.items()}
     os.makedirs(folder, exist_ok=True)
     with open(os.path.join(folder, "config.json"), "w") as handle:
         json.dump(raw, handle)
