@@ -229,7 +229,7 @@ split_attention_kernel(bf16* __restrict__ out, long ld_out, const bf16* __restri
                        const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                        const int* __restrict__ block_table, int max_blocks, const int* __restrict__ positions,
                        const int* __restrict__ token_item, int n_heads, int n_kv_heads, int page_size, float scale,
-                       int window, int chunk, int max_chunks, float* __restrict__ part_acc,
+                       float cap, int window, int chunk, int max_chunks, float* __restrict__ part_acc,
                        float* __restrict__ part_ml, int* __restrict__ counters) {
     constexpr int LPK = D / 8;             // lanes per key: each lane owns 8 of the head's dimensions
     constexpr int KPW = 32 / LPK;          // keys per warp per step
@@ -251,6 +251,8 @@ split_attention_kernel(bf16* __restrict__ out, long ld_out, const bf16* __restri
     unpack8(*reinterpret_cast<const uint4*>(q + (long)t * ld_q + (long)h * D + sub * 8), qf);
     // scores are kept in units of log2(e): exp(x) = 2^(x log2 e) costs one instruction then
     const float scale_log2 = scale * 1.4426950408889634f;
+    // a cap on the scores, cap * tanh(score / cap), in the same units (cap <= 0: none)
+    const float cap_log2 = cap * 1.4426950408889634f, inv_cap_log2 = cap > 0.0f ? 1.0f / cap_log2 : 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         qf[i] *= scale_log2;
@@ -302,6 +304,7 @@ split_attention_kernel(bf16* __restrict__ out, long ld_out, const bf16* __restri
             for (int i = 0; i < 8; i++) dot = fmaf(qf[i], kf[i], dot);
 #pragma unroll
             for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            if (cap > 0.0f) dot = cap_log2 * tanhf(dot * inv_cap_log2);
             sc[u] = valid ? dot : -INFINITY;          // what an absent key left in the ring is never used
             if (!valid) {
 #pragma unroll
@@ -380,12 +383,13 @@ split_attention_kernel(bf16* __restrict__ out, long ld_out, const bf16* __restri
     }
 }
 
-extern "C" int mllm_decode_split_attention(void* out, long ld_out, const void* q, long ld_q, const void* k_pages,
-                                           const void* v_pages, const int* block_table, int max_blocks,
-                                           const int* positions, const int* token_item, int n_tokens, int n_heads,
-                                           int n_kv_heads, int head_size, int page_size, float scale, int window,
-                                           int chunk, int max_chunks, float* part_acc, float* part_ml, int* counters,
-                                           void* stream) {
+// (with a cap on the scores: score <- cap * tanh(score / cap); cap <= 0: none)
+extern "C" int mllm_decode_split_attention_capped(void* out, long ld_out, const void* q, long ld_q, const void* k_pages,
+                                                  const void* v_pages, const int* block_table, int max_blocks,
+                                                  const int* positions, const int* token_item, int n_tokens, int n_heads,
+                                                  int n_kv_heads, int head_size, int page_size, float scale, float cap,
+                                                  int window, int chunk, int max_chunks, float* part_acc, float* part_ml,
+                                                  int* counters, void* stream) {
     if (n_tokens <= 0) return 0;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
         return fail("split_attention: heads must be a multiple of key/value heads");
@@ -397,8 +401,8 @@ extern "C" int mllm_decode_split_attention(void* out, long ld_out, const void* q
 #define LAUNCH_SPLIT(D)                                                                                              \
     launch_kernel(g_dependent_launch != 0, split_attention_kernel<D>, grid, dim3(128), 0, s, (bf16*)out, ld_out,     \
                   (const bf16*)q, ld_q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_blocks,         \
-                  positions, token_item, n_heads, n_kv_heads, page_size, scale, window, chunk, max_chunks, part_acc, \
-                  part_ml, counters)
+                  positions, token_item, n_heads, n_kv_heads, page_size, scale, cap, window, chunk, max_chunks,      \
+                  part_acc, part_ml, counters)
     switch (head_size) {
     case 16: LAUNCH_SPLIT(16); break;
     case 32: LAUNCH_SPLIT(32); break;
@@ -409,6 +413,17 @@ extern "C" int mllm_decode_split_attention(void* out, long ld_out, const void* q
     }
 #undef LAUNCH_SPLIT
     return check_launch("split_attention_kernel");
+}
+
+extern "C" int mllm_decode_split_attention(void* out, long ld_out, const void* q, long ld_q, const void* k_pages,
+                                           const void* v_pages, const int* block_table, int max_blocks,
+                                           const int* positions, const int* token_item, int n_tokens, int n_heads,
+                                           int n_kv_heads, int head_size, int page_size, float scale, int window,
+                                           int chunk, int max_chunks, float* part_acc, float* part_ml, int* counters,
+                                           void* stream) {
+    return mllm_decode_split_attention_capped(out, ld_out, q, ld_q, k_pages, v_pages, block_table, max_blocks, positions,
+                                              token_item, n_tokens, n_heads, n_kv_heads, head_size, page_size, scale, 0.0f,
+                                              window, chunk, max_chunks, part_acc, part_ml, counters, stream);
 }
 
 // Whether split_attention takes a head size (the others run the plain kernel).

@@ -560,7 +560,15 @@ extern "C" int mllm_hybrid_linear_recurrence(const RecurrenceParams* params, int
 //   expert_up    act[pair, f] = silu(W_gate[e] x') * (W_up[e] x') with x' = weight * x
 //   expert_down  hidden[t] += sum over the token's pairs of out_weight * W_down[e] act[pair]
 // Experts are named by a table of pointers (gate, up, down) and inner sizes, so that experts of
-// different sizes (the shared one) go through the same kernels.
+// different sizes (the shared one) go through the same kernels; the down matrices are column
+// ranges of one matrix [width, all inner sizes], so their rows lie ld_down apart.
+//
+// For many tokens the same sum runs as two products over ALL experts: gates and ups of every
+// expert as one matrix, the down matrices side by side as another.  An expert a token did not
+// choose gets the input weight 0, and expert(0) = W_down (silu(0) * 0) = 0 exactly; the input
+// weight multiplies the product's result instead of its input (W (s x) = s (W x)):
+//   expert_combine   act[t, c] = silu(s G[t, c]) * (s U[t, c]) * out_weight for column c of expert e,
+//                    s = the token's input weight for e, or 0
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -642,7 +650,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 expert_down_kernel(float* __restrict__ hidden, long ld_hidden, const T* __restrict__ act, long ld_act,
                    const int* __restrict__ choice, const float* __restrict__ out_weight, const long long* __restrict__ down_of,
-                   const int* __restrict__ inner_of, int width, int pairs) {
+                   const int* __restrict__ inner_of, long ld_down, int width, int pairs) {
     dependents_may_start();
     wait_for_earlier_kernels();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -652,7 +660,7 @@ expert_down_kernel(float* __restrict__ hidden, long ld_hidden, const T* __restri
             const long pair = (long)t * pairs + k;
             const int e = choice[pair];
             const int inner = inner_of[e];
-            const T* w = (const T*)down_of[e] + (long)c * inner;
+            const T* w = (const T*)down_of[e] + (long)c * ld_down;
             const T* a = act + pair * ld_act;
             float z = 0.0f;
             for (int f = lane; f < inner; f += 32) z = fmaf(to_f32(w[f]), to_f32(a[f]), z);
@@ -660,6 +668,54 @@ expert_down_kernel(float* __restrict__ hidden, long ld_hidden, const T* __restri
         }
         if (lane == 0) hidden[(long)t * ld_hidden + c] += total;
     }
+}
+
+// gu: [T, 2 * total] = [gates of all experts | ups of all experts]; act: [T, total].  Columns
+// [e * inner, (e + 1) * inner) belong to routed expert e, columns from n_experts * inner on to the
+// shared expert (pair index `top` of every token, if there is one).
+template <typename T>
+__global__ void __launch_bounds__(256)
+expert_combine_kernel(T* __restrict__ act, long ld_act, const T* __restrict__ gu, long ld_gu, const int* __restrict__ choice,
+                      const float* __restrict__ in_weight, const float* __restrict__ out_weight, int n_experts, int inner,
+                      int total, int top, int pairs) {
+    dependents_may_start();
+    wait_for_earlier_kernels();
+    const int t = blockIdx.x;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < total; c += gridDim.y * blockDim.x) {
+        const int e = c < n_experts * inner ? c / inner : n_experts;
+        float s = 0.0f, o = 1.0f;
+        if (e == n_experts) {
+            s = in_weight[(long)t * pairs + top], o = out_weight[(long)t * pairs + top];
+        } else {
+            for (int k = 0; k < top; k++)
+                if (choice[(long)t * pairs + k] == e) s = in_weight[(long)t * pairs + k];
+        }
+        float v = 0.0f;
+        if (s != 0.0f) {
+            const float g = s * to_f32(gu[(long)t * ld_gu + c]), u = s * to_f32(gu[(long)t * ld_gu + total + c]);
+            v = silu_f(g) * u * o;
+        }
+        act[(long)t * ld_act + c] = from_f32<T>(v);
+    }
+}
+
+extern "C" int mllm_hybrid_expert_combine(void* act, long ld_act, const void* gu, long ld_gu, const int* choice,
+                                          const float* in_weight, const float* out_weight, int n_experts, int inner, int total,
+                                          int top, int pairs, int n_tokens, int dtype, void* stream) {
+    if (n_tokens <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    int y = (total + 255) / 256;
+    if (y > 64) y = 64;
+    dim3 grid(n_tokens, y);
+    if (dtype == DT_F32)
+        launch_kernel(g_dependent_launch != 0, expert_combine_kernel<float>, grid, dim3(256), 0, s, (float*)act, ld_act,
+                      (const float*)gu, ld_gu, choice, in_weight, out_weight, n_experts, inner, total, top, pairs);
+    else if (dtype == DT_BF16)
+        launch_kernel(g_dependent_launch != 0, expert_combine_kernel<bf16>, grid, dim3(256), 0, s, (bf16*)act, ld_act,
+                      (const bf16*)gu, ld_gu, choice, in_weight, out_weight, n_experts, inner, total, top, pairs);
+    else
+        return fail("expert_combine: unknown dtype");
+    return check_launch("expert_combine_kernel");
 }
 
 extern "C" int mllm_hybrid_route(const void* x, long ld_x, const void* router, const void* shared_gate, int width, int n_experts,
@@ -684,7 +740,8 @@ extern "C" int mllm_hybrid_route(const void* x, long ld_x, const void* router, c
 extern "C" int mllm_hybrid_experts(float* hidden, long ld_hidden, void* act, long ld_act, const void* x, long ld_x,
                                    const int* choice, const float* in_weight, const float* out_weight,
                                    const long long* gate_of, const long long* up_of, const long long* down_of,
-                                   const int* inner_of, int max_inner, int width, int pairs, int n_tokens, int dtype, void* stream) {
+                                   const int* inner_of, long ld_down, int max_inner, int width, int pairs, int n_tokens,
+                                   int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t shared = sizeof(float) * (size_t)width;
@@ -698,12 +755,12 @@ extern "C" int mllm_hybrid_experts(float* hidden, long ld_hidden, void* act, lon
         launch_kernel(g_dependent_launch != 0, expert_up_kernel<float>, up_grid, dim3(256), shared, s, (float*)act, ld_act,
                       (const float*)x, ld_x, choice, in_weight, gate_of, up_of, inner_of, width, pairs);
         launch_kernel(g_dependent_launch != 0, expert_down_kernel<float>, down_grid, dim3(256), 0, s, hidden, ld_hidden,
-                      (const float*)act, ld_act, choice, out_weight, down_of, inner_of, width, pairs);
+                      (const float*)act, ld_act, choice, out_weight, down_of, inner_of, ld_down, width, pairs);
     } else if (dtype == DT_BF16) {
         launch_kernel(g_dependent_launch != 0, expert_up_kernel<bf16>, up_grid, dim3(256), shared, s, (bf16*)act, ld_act,
                       (const bf16*)x, ld_x, choice, in_weight, gate_of, up_of, inner_of, width, pairs);
         launch_kernel(g_dependent_launch != 0, expert_down_kernel<bf16>, down_grid, dim3(256), 0, s, hidden, ld_hidden,
-                      (const bf16*)act, ld_act, choice, out_weight, down_of, inner_of, width, pairs);
+                      (const bf16*)act, ld_act, choice, out_weight, down_of, inner_of, ld_down, width, pairs);
     } else {
         return fail("experts: unknown dtype");
     }

@@ -111,20 +111,22 @@ extern "C" int mllm_sequence_grouped_rms_norm(void* out, long ld_out, const floa
 // if `silu` is set.  h and out may have row strides of their own (columns of a wider buffer),
 // and out may be h: a block reads its token's earlier rows, so a second buffer is needed only
 // when a step brings more than one token of a request (the launcher's caller sees to that).
-// One block per token.  A second kernel (one block per entry) then moves the state on.
+// One block per token.  A second kernel (one block per entry) then moves the state on; in a step
+// of single tokens (writes == 2) the first kernel moves it itself.
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void causal_taps_kernel(T* __restrict__ out, long ld_out, const T* __restrict__ h, long ld_h,
                                    const float* __restrict__ w, const float* __restrict__ bias,
-                                   const float* __restrict__ state, long state_stride, const int* __restrict__ positions,
+                                   float* state, long state_stride, const int* __restrict__ positions,
                                    const int* __restrict__ token_item, const int* __restrict__ item_slot,
-                                   const int* __restrict__ item_start, int width, int taps, int identity, int silu) {
+                                   const int* __restrict__ item_start, int width, int taps, int identity, int silu,
+                                   int moves_state) {
     dependents_may_start();
     wait_for_earlier_kernels();
     const int t = blockIdx.x;
     const int item = token_item[t];
     const int local = positions[t] - item_start[item];          // tokens of this request before t in this step
-    const float* held = state + (long)item_slot[item] * state_stride;
+    float* held = state + (long)item_slot[item] * state_stride;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         const float mine = to_f32(h[(long)t * ld_h + c]);
         float acc = identity ? mine : 0.0f;
@@ -138,6 +140,11 @@ __global__ void causal_taps_kernel(T* __restrict__ out, long ld_out, const T* __
         acc = fmaf(w[(long)c * taps + taps - 1], mine, acc);
         if (silu) acc = silu_f(acc);
         out[(long)t * ld_out + c] = from_f32<T>(acc);
+        if (moves_state) {
+            // a step of single tokens: this thread is the only one that touches the channel's state
+            for (int s = 0; s + 1 < taps - 1; s++) held[(long)s * width + c] = held[(long)(s + 1) * width + c];
+            if (taps > 1) held[(long)(taps - 2) * width + c] = mine;
+        }
     }
 }
 
@@ -232,15 +239,15 @@ extern "C" int mllm_sequence_causal_taps(void* out, long ld_out, const void* h, 
     if (dtype == DT_F32) {
         launch_kernel(g_dependent_launch != 0, causal_taps_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (float*)out, ld_out,
                       (const float*)h, ld_h, w, bias, state, state_stride, positions, token_item, item_slot, item_start, width,
-                      taps, identity, silu);
-        if (writes && taps > 1)
+                      taps, identity, silu, (int)(writes == 2));
+        if (writes == 1 && taps > 1)
             launch_kernel(g_dependent_launch != 0, causal_taps_state_kernel<float>, dim3(n_items), dim3(threads), 0, s, state,
                           state_stride, (const float*)h, ld_h, item_slot, item_offset, item_count, width, taps);
     } else if (dtype == DT_BF16) {
         launch_kernel(g_dependent_launch != 0, causal_taps_kernel<bf16>, dim3(n_tokens), dim3(threads), 0, s, (bf16*)out, ld_out,
                       (const bf16*)h, ld_h, w, bias, state, state_stride, positions, token_item, item_slot, item_start, width,
-                      taps, identity, silu);
-        if (writes && taps > 1)
+                      taps, identity, silu, (int)(writes == 2));
+        if (writes == 1 && taps > 1)
             launch_kernel(g_dependent_launch != 0, causal_taps_state_kernel<bf16>, dim3(n_items), dim3(threads), 0, s, state,
                           state_stride, (const bf16*)h, ld_h, item_slot, item_offset, item_count, width, taps);
     } else {

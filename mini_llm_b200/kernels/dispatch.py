@@ -107,9 +107,10 @@ class Kernels:
                 return ops.norm_taps_step(out, h.x, h.gain, h.groups, h.eps, w, state, ctx.token_item, ctx.item_slot, writes)
             h = h.materialize(ctx)
         self.chose("causal_taps", "causal_taps", out.shape[0], out.shape[1], w.shape[1])
-        self.launches += 2 if writes and w.shape[1] > 1 else 1
+        single = bool(ctx.decode_only)            # every entry brings one token: the filter's kernel moves the state too
+        self.launches += 2 if writes and w.shape[1] > 1 and not single else 1
         return ops.causal_taps(out, h, w, state, ctx.positions, ctx.token_item, ctx.item_slot, ctx.item_start,
-                               ctx.item_offset, ctx.item_count, writes, identity, bias, silu)
+                               ctx.item_offset, ctx.item_count, writes, identity, bias, silu, single)
 
     # ---- rotary positions with the cache store, capped attention, linear recurrences, routed experts ----
     def rotary_store(self, ctx, cache, qkv, k_off, v_off, heads, kv_heads, dim, vdim, rot_dims, inv_freq, amplitude):
@@ -123,6 +124,19 @@ class Kernels:
         share the cached rows they read); steps of single tokens, and sizes the tiles do not take,
         one block per (token, head)."""
         self.launches += 1
+        n = q.shape[0]
+        if (not self.plain_only and ctx.decode_only and n <= SPLIT_ATTENTION_MAX_ROWS and dim == vdim
+                and dim in ops.SPLIT_ATTENTION_HEAD_SIZES and q.dtype == torch.bfloat16 and q.stride(0) % 8 == 0):
+            # single tokens: each token's keys in chunks over many CTAs, merged by the last to arrive
+            # (its exponentials, weights and sums are 32-bit, which this attention asks for)
+            pairs = n * n_heads
+            chunk = 64 if pairs < 64 else (128 if pairs < 128 else (256 if pairs < 256 else 512))
+            reach = cache.block_table.shape[1] * cache.page_size
+            acc, ml, counters = self._scratch(ctx, SPLIT_ATTENTION_MAX_ROWS * n_heads, -(-reach // 64), dim)
+            self.chose("capped_attention", "split_attention", n, n_heads, dim, vdim)
+            return ops.split_attention(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions, ctx.token_item,
+                                       n_heads, n_kv_heads, dim, cache.page_size, scale, window, chunk, -(-reach // chunk), acc,
+                                       ml, counters, cap=cap)
         tiled = not ctx.decode_only and ops.capped_attention_tiled_takes(dim, vdim)
         self.chose("capped_attention", "capped_attention_tiled" if tiled else "capped_attention_plain", q.shape[0], n_heads, dim, vdim)
         return ops.capped_attention(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions, ctx.token_item,
@@ -138,9 +152,24 @@ class Kernels:
         self.launches += 1
         return ops.route(x, router, shared_gate, top, choice, in_weight, out_weight)
 
-    def experts(self, hidden, act, x, choice, in_weight, out_weight, gate_of, up_of, down_of, inner_of, max_inner, pairs):
+    def experts(self, hidden, act, x, choice, in_weight, out_weight, gate_of, up_of, down_of, inner_of, max_inner, pairs,
+                ld_down=None):
         self.launches += 2
-        return ops.experts(hidden, act, x, choice, in_weight, out_weight, gate_of, up_of, down_of, inner_of, max_inner, pairs)
+        return ops.experts(hidden, act, x, choice, in_weight, out_weight, gate_of, up_of, down_of, inner_of, max_inner, pairs,
+                           ld_down)
+
+    EXPERTS_AT_ONCE_TOKENS = 32    # from here on a step's tokens go through all experts as two products
+
+    def experts_at_once(self, n_tokens, x, up_matrix, down_matrix) -> bool:
+        """Whether the routed feed-forward of this step runs as two tensor-core products over all
+        experts (unchosen experts weigh 0) instead of pair by pair: many tokens, bfloat16, shapes
+        the product kernel takes."""
+        return (not self.plain_only and n_tokens >= self.EXPERTS_AT_ONCE_TOKENS and isinstance(x, torch.Tensor)
+                and ops.gemm_takes(x, up_matrix) and down_matrix.shape[1] % 8 == 0 and down_matrix.shape[0] >= 16)
+
+    def expert_combine(self, act, gu, choice, in_weight, out_weight, n_experts, inner, top, pairs):
+        self.launches += 1
+        return ops.expert_combine(act, gu, choice, in_weight, out_weight, n_experts, inner, top, pairs)
 
     def scaled_add(self, x, u, a, v=None, b=0.0):
         self.launches += 1

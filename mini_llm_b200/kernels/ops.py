@@ -228,8 +228,8 @@ class _SkinnyParams(ctypes.Structure):
 
 
 _skinny = Function("decode", "mllm_decode_skinny_linear", [ctypes.POINTER(_SkinnyParams), P])
-_split_attention = Function("decode", "mllm_decode_split_attention",
-                            [P, L, P, L, P, P, P, I, P, P, I, I, I, I, I, F, I, I, I, P, P, P, P])
+_split_attention = Function("decode", "mllm_decode_split_attention_capped",
+                            [P, L, P, L, P, P, P, I, P, P, I, I, I, I, I, F, F, I, I, I, P, P, P, P])
 
 SKINNY_MAX_SMEM = 200 * 1024
 SPLIT_ATTENTION_HEAD_SIZES = (16, 32, 64, 128, 256)
@@ -303,10 +303,11 @@ def skinny_linear(out, x, w, bias=None, epilogue="store", norm=None, scatter=Non
 
 
 def split_attention(out, q, k_pages, v_pages, block_table, positions, token_item, n_heads, n_kv_heads, head_size,
-                    page_size, scale, window, chunk, max_chunks, part_acc, part_ml, counters):
+                    page_size, scale, window, chunk, max_chunks, part_acc, part_ml, counters, cap=0.0):
     """Causal attention over the paged cache for few tokens: one CTA per (token, head, chunk
     of ``chunk`` keys); needs fp32 scratch ``part_acc`` [T*H*max_chunks*D], ``part_ml``
-    [T*H*max_chunks*2] and zeroed int32 ``counters`` [T*H] (left zero)."""
+    [T*H*max_chunks*2] and zeroed int32 ``counters`` [T*H] (left zero).  ``cap`` > 0: the scores
+    are capped, cap * tanh(score / cap).  Scores, weights and sums are 32-bit."""
     _check(out, "split_attention.out", torch.bfloat16, 2)
     _check(q, "split_attention.q", torch.bfloat16, 2)
     _check(k_pages, "split_attention.k_pages", torch.bfloat16)
@@ -327,7 +328,7 @@ def split_attention(out, q, k_pages, v_pages, block_table, positions, token_item
         raise KernelError("split_attention: the chunks do not cover the longest block table")
     _split_attention(out.data_ptr(), out.stride(0), q.data_ptr(), q.stride(0), k_pages.data_ptr(), v_pages.data_ptr(),
                      block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), token_item.data_ptr(), n,
-                     n_heads, n_kv_heads, head_size, page_size, float(scale), int(window or 0), int(chunk),
+                     n_heads, n_kv_heads, head_size, page_size, float(scale), float(cap or 0.0), int(window or 0), int(chunk),
                      int(max_chunks), part_acc.data_ptr(), part_ml.data_ptr(), counters.data_ptr(), _stream())
     return out
 
@@ -826,12 +827,13 @@ _causal_taps = Function("sequence", "mllm_sequence_causal_taps",
 
 
 def causal_taps(out, h, w, state, positions, token_item, item_slot, item_start, item_offset, item_count, writes=True,
-                identity=True, bias=None, silu=False):
+                identity=True, bias=None, silu=False, single_tokens=False):
     """out[t] = act(h[t] + bias + sum_j w[:, j] * h[t - (taps - 1) + j]) over the tokens of one request, per
     channel; what lies before this step's portion comes from ``state`` [slots, taps - 1, width]
     (fp32, oldest first), which is then moved on by this step's tokens (unless ``writes`` is false).
     ``identity`` false: the input itself is not added (a plain convolution); ``bias`` [width] fp32 or
-    None; ``silu``: the activation.  ``h`` and ``out`` may be column ranges of wider buffers."""
+    None; ``silu``: the activation.  ``h`` and ``out`` may be column ranges of wider buffers.
+    ``single_tokens``: every entry brings one token; the state is then moved by the same kernel."""
     _check(out, "causal_taps.out", h.dtype, 2)
     _check(h, "causal_taps.h", None, 2)
     _check(w, "causal_taps.w", torch.float32, 2)
@@ -851,8 +853,8 @@ def causal_taps(out, h, w, state, positions, token_item, item_slot, item_start, 
         raise KernelError(f"causal_taps: the state must be [slots, {taps - 1}, {width}]")
     _causal_taps(out.data_ptr(), out.stride(0), h.data_ptr(), h.stride(0), w.data_ptr(), _ptr(bias), state.data_ptr(),
                  state.stride(0), positions.data_ptr(), token_item.data_ptr(), item_slot.data_ptr(), item_start.data_ptr(),
-                 item_offset.data_ptr(), item_count.data_ptr(), n, item_count.shape[0], width, taps, int(bool(writes)),
-                 int(bool(identity)), int(bool(silu)), dtype_code(h.dtype), _stream())
+                 item_offset.data_ptr(), item_count.data_ptr(), n, item_count.shape[0], width, taps,
+                 (2 if single_tokens else 1) if writes else 0, int(bool(identity)), int(bool(silu)), dtype_code(h.dtype), _stream())
     return out
 
 
@@ -1261,7 +1263,8 @@ def linear_recurrence(out, q, k, v, gate_a, gate_b, log_rate, step_bias, state, 
 
 
 _route = Function("hybrid", "mllm_hybrid_route", [P, L, P, P, I, I, I, P, P, P, I, I, P])
-_experts = Function("hybrid", "mllm_hybrid_experts", [P, L, P, L, P, L, P, P, P, P, P, P, P, I, I, I, I, I, P])
+_experts = Function("hybrid", "mllm_hybrid_experts", [P, L, P, L, P, L, P, P, P, P, P, P, P, L, I, I, I, I, I, P])
+_expert_combine = Function("hybrid", "mllm_hybrid_expert_combine", [P, L, P, L, P, P, P, I, I, I, I, I, I, I, P])
 
 
 def route(x, router, shared_gate, top, choice, in_weight, out_weight):
@@ -1286,11 +1289,12 @@ def route(x, router, shared_gate, top, choice, in_weight, out_weight):
            in_weight.data_ptr(), out_weight.data_ptr(), n, dtype_code(x.dtype), _stream())
 
 
-def experts(hidden, act, x, choice, in_weight, out_weight, gate_of, up_of, down_of, inner_of, max_inner, pairs):
+def experts(hidden, act, x, choice, in_weight, out_weight, gate_of, up_of, down_of, inner_of, max_inner, pairs, ld_down=None):
     """hidden[t] += sum over the token's ``pairs`` of out_weight * W_down[e] (silu(W_gate[e] x') * (W_up[e] x')),
     x' = in_weight * x[t] rounded to the activations' type; expert e's matrices are named by the
-    int64 pointer tables ``gate_of``, ``up_of``, ``down_of`` and its inner size by ``inner_of`` (int32).
-    ``act`` [T * pairs, max_inner] is scratch."""
+    int64 pointer tables ``gate_of``, ``up_of``, ``down_of`` and its inner size by ``inner_of`` (int32);
+    the rows of every down matrix lie ``ld_down`` elements apart (None: ``max_inner``, for experts of
+    one size that are stored each by itself).  ``act`` [T * pairs, max_inner] is scratch."""
     _check(hidden, "experts.hidden", torch.float32, 2)
     _check(x, "experts.x", None, 2)
     _check(act, "experts.act", x.dtype, 2)
@@ -1302,8 +1306,24 @@ def experts(hidden, act, x, choice, in_weight, out_weight, gate_of, up_of, down_
         raise KernelError("experts: sizes do not agree")
     _experts(hidden.data_ptr(), hidden.stride(0), act.data_ptr(), act.stride(0), x.data_ptr(), x.stride(0), choice.data_ptr(),
              in_weight.data_ptr(), out_weight.data_ptr(), gate_of.data_ptr(), up_of.data_ptr(), down_of.data_ptr(),
-             inner_of.data_ptr(), int(max_inner), width, int(pairs), n, dtype_code(x.dtype), _stream())
+             inner_of.data_ptr(), int(ld_down if ld_down is not None else max_inner), int(max_inner), width, int(pairs), n,
+             dtype_code(x.dtype), _stream())
     return hidden
+
+
+def expert_combine(act, gu, choice, in_weight, out_weight, n_experts, inner, top, pairs):
+    """For the products over all experts at once: ``gu`` [T, 2 * total] holds every expert's gate and
+    up results ([gates | ups], routed expert e in columns [e * inner, (e + 1) * inner), the shared
+    expert behind them); act[t, c] = silu(s g) * (s u) * out_weight with s the token's input weight
+    for the column's expert, or 0 for an expert it did not choose.  act: [T, total]."""
+    _check(act, "expert_combine.act", gu.dtype, 2)
+    _check(gu, "expert_combine.gu", None, 2)
+    n, total = act.shape
+    if gu.shape != (n, 2 * total) or total < n_experts * inner or (pairs == top and total != n_experts * inner):
+        raise KernelError("expert_combine: sizes do not agree")
+    _expert_combine(act.data_ptr(), act.stride(0), gu.data_ptr(), gu.stride(0), choice.data_ptr(), in_weight.data_ptr(),
+                    out_weight.data_ptr(), n_experts, inner, total, top, pairs, n, dtype_code(gu.dtype), _stream())
+    return act
 
 
 _scaled_add = Function("hybrid", "mllm_hybrid_scaled_add", [P, P, F, P, F, L, P])

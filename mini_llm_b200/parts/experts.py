@@ -8,7 +8,11 @@ the same form (with an inner size of its own) may run for every token; its outpu
 by ``sigmoid(w_sg . x)``, one number per token.
 
 Experts are named by tables of pointers and inner sizes, so the shared expert goes through the
-kernels as one more chosen expert with input weight 1 and its gate as the output weight.
+kernels as one more chosen expert with input weight 1 and its gate as the output weight.  A step
+of few tokens runs pair by pair (token, chosen expert) and reads only the chosen experts'
+matrices.  A step of many tokens runs two products over all experts at once: an expert a token
+did not choose weighs 0 there, ``expert(0) = 0`` exactly, and the score multiplies the result
+of the first product instead of its input (``W (s x) = s (W x)``).
 """
 
 from __future__ import annotations
@@ -57,14 +61,29 @@ class RoutedExperts(FeedForward):
         super().bind(tensors, runtime)
         n = self.names
         experts = self._expert_names()
-        device = self.w(n["router"]).device
+        router = self.w(n["router"])
+        device = router.device
+        # All gates, then all ups, as the rows of one matrix; all down matrices side by side as the
+        # columns of another.  An expert's own matrices are row and column ranges of these (the pair
+        # kernels get them by pointer), so a step of many tokens can run two products over all
+        # experts and a step of few tokens reads only the experts it chose, from the same memory.
+        self.total = sum(inner for _, inner in experts)
+        self.up_matrix = torch.cat([self.w(f"{name}.{n[which]}") for which in ("gate", "up") for name, _ in experts]).contiguous()
+        self.down_matrix = torch.cat([self.w(f"{name}.{n['down']}") for name, _ in experts], dim=1).contiguous()
+        starts = [sum(inner for _, inner in experts[:e]) for e in range(len(experts))]
+        size = self.up_matrix.element_size()
 
-        def table(which):
-            return torch.tensor([self.w(f"{name}.{n[which]}").data_ptr() for name, _ in experts], dtype=torch.int64, device=device)
+        def table(base, offsets):
+            return torch.tensor([base + offset * size for offset in offsets], dtype=torch.int64, device=device)
 
-        self.gate_of, self.up_of, self.down_of = table("gate"), table("up"), table("down")
+        self.gate_of = table(self.up_matrix.data_ptr(), [start * self.width for start in starts])
+        self.up_of = table(self.up_matrix.data_ptr(), [(self.total + start) * self.width for start in starts])
+        self.down_of = table(self.down_matrix.data_ptr(), starts)
         self.inner_of = torch.tensor([inner for _, inner in experts], dtype=torch.int32, device=device)
         self.max_inner = max(inner for _, inner in experts)
+        # the loaded matrices are held in the stacked ones now
+        self.weights = {name: tensor for name, tensor in self.weights.items()
+                        if name in (self.full_name(n["router"]), self.full_name(n["shared_gate"]))}
 
     def forward(self, ctx, x, hidden):
         k, n = ctx.kernels, x.shape[0]
@@ -73,9 +92,16 @@ class RoutedExperts(FeedForward):
         out_weight = ctx.buffer("expert_out_weight", (n * self.pairs,), torch.float32)
         k.route(x, self.w(self.names["router"]), self.w(self.names["shared_gate"]) if self.shared_inner else None, self.top,
                 choice, in_weight, out_weight)
+        if k.experts_at_once(n, x, self.up_matrix, self.down_matrix):
+            gu = ctx.buffer("expert_gate_up", (n, 2 * self.total), ctx.act_dtype)
+            k.linear(ctx, gu, x, self.up_matrix)
+            act = ctx.buffer("expert_act_all", (n, self.total), ctx.act_dtype)
+            k.expert_combine(act, gu, choice, in_weight, out_weight, self.n_experts, self.inner, self.top, self.pairs)
+            k.linear(ctx, hidden, act, self.down_matrix, None, epilogue="add")
+            return
         act = ctx.buffer("expert_act", (n * self.pairs, self.max_inner), ctx.act_dtype)
         k.experts(hidden, act, x, choice, in_weight, out_weight, self.gate_of, self.up_of, self.down_of, self.inner_of,
-                  self.max_inner, self.pairs)
+                  self.max_inner, self.pairs, ld_down=self.total)
 
     def compute(self, ctx, x):
         out = ctx.buffer("mlp_out", (x.shape[0], self.width), torch.float32)

@@ -386,6 +386,40 @@ def test_attention_in_tiles_against_one_block_per_row(heads, kv_heads, dim, vdim
         torch.testing.assert_close(want[row, head * vdim:(head + 1) * vdim].double(), expected, rtol=1e-4, atol=1e-5)
 
 
+@pytest.mark.parametrize("heads, kv_heads, size, cap", [(4, 2, 64, 5.0), (6, 1, 128, 0.0), (3, 3, 32, 1.5)])
+def test_single_tokens_over_split_keys_with_a_cap(heads, kv_heads, size, cap):
+    """A step of single tokens in bfloat16: each token's keys in chunks over many blocks, with the cap
+    on the scores, against the kernel with one block per (token, head)."""
+    from mini_llm_b200.kernels import ops
+    torch.manual_seed(size + heads)
+    page_size, lengths = 16, [700, 1, 130, 64]
+    blocks = [-(-n // page_size) for n in lengths]
+    k_pages = torch.randn(sum(blocks) + 1, page_size, kv_heads, size, device="cuda").bfloat16()
+    v_pages = torch.randn(sum(blocks) + 1, page_size, kv_heads, size, device="cuda").bfloat16()
+    order = torch.randperm(sum(blocks)).tolist()
+    table = torch.zeros(len(lengths), max(blocks), dtype=torch.int32)
+    at = 0
+    for i, count in enumerate(blocks):
+        table[i, :count] = torch.tensor(order[at:at + count], dtype=torch.int32)
+        at += count
+    table = table.cuda()
+    n = len(lengths)
+    positions = dev([length - 1 for length in lengths], torch.int32)
+    token_item = dev(list(range(n)), torch.int32)
+    q = (torch.randn(n, heads * size, device="cuda") * 0.5).bfloat16()
+    want = torch.empty(n, heads * size, device="cuda", dtype=torch.bfloat16)
+    ops.capped_attention(want, q, k_pages, v_pages, table, positions, token_item, heads, kv_heads, size, size, page_size, 0.3, cap)
+    chunk, reach = 64, table.shape[1] * page_size
+    chunks = -(-reach // chunk)
+    scratch = (torch.empty(n * heads * chunks * size, device="cuda"), torch.empty(n * heads * chunks * 2, device="cuda"),
+               torch.zeros(n * heads, dtype=torch.int32, device="cuda"))
+    got = torch.full_like(want, float("nan"))
+    ops.split_attention(got, q, k_pages, v_pages, table, positions, token_item, heads, kv_heads, size, page_size, 0.3, 0, chunk,
+                        chunks, *scratch, cap=cap)
+    torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+    assert int(scratch[2].abs().max()) == 0
+
+
 def test_rotation_and_cache_store():
     from mini_llm_b200.kernels import ops
     from mini_llm_b200.parts.rotary import rotary_frequencies
@@ -441,6 +475,15 @@ def test_router_and_expert_kernels():
         assert int(choice[t * pairs + top]) == experts
     hidden = torch.ones((n, width), device="cuda")
     act = torch.empty((n * pairs, shared_inner), device="cuda")
-    ops.experts(hidden, act, dev(x), choice, in_weight, out_weight, table("gate"), table("up"), table("down"),
-                dev([inner] * experts + [shared_inner], torch.int32), shared_inner, pairs)
+    down_all = torch.cat([held[f"m.{name}.down"] for name in names], dim=1).contiguous()        # side by side, rows 92 apart
+    starts = [e * inner for e in range(experts)] + [experts * inner]
+    down_of = torch.tensor([down_all.data_ptr() + 4 * start for start in starts], dtype=torch.int64, device="cuda")
+    ops.experts(hidden, act, dev(x), choice, in_weight, out_weight, table("gate"), table("up"), down_of,
+                dev([inner] * experts + [shared_inner], torch.int32), shared_inner, pairs, ld_down=down_all.shape[1])
     np.testing.assert_allclose(hidden.cpu().numpy() - 1.0, expected, atol=2e-5)
+    # the same through the products over all experts: gates and ups of every expert, unchosen ones weighed 0
+    up_all = torch.cat([held[f"m.{name}.{which}"] for which in ("gate", "up") for name in names])
+    gu = dev(x) @ up_all.T
+    combined = torch.empty((n, down_all.shape[1]), device="cuda")
+    ops.expert_combine(combined, gu.contiguous(), choice, in_weight, out_weight, experts, inner, top, pairs)
+    np.testing.assert_allclose((combined @ down_all.T).cpu().numpy(), expected, atol=2e-5)
