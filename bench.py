@@ -64,9 +64,11 @@ def parse_args():
     parser.add_argument("--kernels", action="store_true",
                         help="time single kernels (matrix products at forced tile widths, prompt attention) back to "
                              "back in a replayed graph and print one line each: the tables of profiles/ come from this")
-    parser.add_argument("--compare", default=None, choices=("fuvolix",),
-                        help="prefill and decode of Fuvolix stacks at sizes of real layers (random weights), beside GPT-2 "
-                             "of equal width, depth and inner size, and their mixers' kernels alone; one line each")
+    parser.add_argument("--compare", default=None, choices=("fuvolix", "sumozen"),
+                        help="fuvolix: prefill and decode of Fuvolix stacks at sizes of real layers (random weights), beside "
+                             "GPT-2 of equal width, depth and inner size, and their mixers' kernels alone; sumozen: Sumozen "
+                             "stacks beside Fuvolix stacks of equal width, depth and inner size, and its kernels alone; "
+                             "one line each")
     parser.add_argument("--tokens-out", default=None,
                         help="(--impl reference) write the greedy tokens of the fixed check workload to this file "
                              "and print nothing else")
@@ -892,6 +894,209 @@ def mixer_kernels(torch, size: dict, peak: dict):
     return lines
 
 
+# Sumozen stacks beside Fuvolix of equal width, depth and inner size: layers in threes (two with an
+# attention and a gated delta rule side by side, one state-space layer), every layer with a routed
+# feed-forward whose chosen experts plus the shared one have the inner size of the dense one.
+SUMOZEN_SIZES = {
+    "small": {"width": 768, "layers": 12, "ff": 3072, "fuvolix": "small",
+              "left": {"heads": 12, "kv_heads": 4, "dim": 64, "vdim": 64}, "right": {"heads": 6, "kv_heads": 3, "dim": 128, "vdim": 128},
+              "mamba": {"heads": 24, "vdim": 64, "state": 128, "groups": 1, "norm_groups": 1},
+              "moe": {"experts": 8, "top": 2, "ff": 768, "shared": 1536}},
+    "medium": {"width": 1024, "layers": 24, "ff": 4096, "fuvolix": "medium",
+               "left": {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 64}, "right": {"heads": 8, "kv_heads": 4, "dim": 128, "vdim": 128},
+               "mamba": {"heads": 32, "vdim": 64, "state": 128, "groups": 1, "norm_groups": 1},
+               "moe": {"experts": 8, "top": 2, "ff": 1024, "shared": 2048}},
+}
+
+
+def sumozen_config(size: dict, vocab: int) -> dict:
+    left, right, moe = size["left"], size["right"], size["moe"]
+    mlp = {"kind": "moe", "router": {"experts": moe["experts"], "top": moe["top"]}, "expert": {"ff": moe["ff"]},
+           "shared": {"ff": moe["shared"]}}
+    parallel = {"type": "parallel", "mlp": mlp, "mixer": {
+        "left": dict(left, conv=4, scale=left["dim"] ** -0.5, softcap=50.0,
+                     rot={"base": 10000.0, "dims": left["dim"], "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}}),
+        "right": dict(right, conv=4), "left_scale": 1.0, "right_scale": 1.0}}
+    mamba = {"type": "mamba2", "mlp": mlp, "mixer": dict(size["mamba"], conv=4)}
+    three = [parallel, parallel, mamba]
+    return {"architecture": "Sumozen", "vocab": vocab, "width": size["width"], "norm": {"eps": 1e-5},
+            "layers": [three[i % 3] for i in range(size["layers"])]}
+
+
+def sumozen_kernels(torch, size: dict, peak: dict):
+    """Sumozen's kernels alone, replayed back to back on operands of their own: prompt portions
+    (2 x 1,024 tokens) and single tokens (8 requests at 1,023 cached tokens), each with the work it
+    must do and the fraction of its bound: 32-bit FMA (nominal) where the sums are 32-bit by the
+    design's rule, measured HBM copy bandwidth where the state, the cache or the weights are
+    streamed, measured bf16 throughput for the products."""
+    from mini_llm_b200.kernels import ops
+    lines = []
+    page, fma_peak = 64, FP32_FMA_TFLOPS_NOMINAL
+    dev = lambda values: torch.tensor(values, dtype=torch.int32, device="cuda")
+
+    def add(kernel, us, flops=None, bytes_moved=None, tensor_flops=None, **more):
+        line = {"kernel": kernel, "us": round(us, 2), **more}
+        if flops is not None:
+            line.update(tflops=round(flops / us / 1e6, 2), frac_fp32_fma_nominal=round(flops / us / 1e6 / fma_peak, 3))
+        if tensor_flops is not None:
+            line.update(tflops=round(tensor_flops / us / 1e6, 2), frac_bf16_measured=round(tensor_flops / us / 1e6 / peak["bf16_tflops"], 3))
+        if bytes_moved is not None:
+            line.update(gbs=round(bytes_moved / us / 1e3, 1), frac_hbm_measured=round(bytes_moved / us / 1e3 / peak["hbm_gbs"], 3))
+        lines.append(line)
+
+    # ---- the attention with capped scores ----
+    left = size["left"]
+    heads, kv_heads, dim, vdim = left["heads"], left["kv_heads"], left["dim"], left["vdim"]
+    for name, lengths, new in (("prompts, 2 x 1024", [1024, 1024], [1024, 1024]), ("single tokens, 8 x 1024", [1024] * 8, [1] * 8)):
+        blocks = [-(-n // page) for n in lengths]
+        table = torch.zeros(len(lengths), max(blocks), dtype=torch.int32)
+        at = 0
+        for i, count in enumerate(blocks):
+            table[i, :count] = torch.arange(at, at + count, dtype=torch.int32)
+            at += count
+        table = table.cuda()
+        n = sum(new)
+        starts = [length - count for length, count in zip(lengths, new)]
+        positions = torch.cat([torch.arange(s, s + m) for s, m in zip(starts, new)]).int().cuda()
+        token_item = torch.cat([torch.full((m,), i) for i, m in enumerate(new)]).int().cuda()
+        pairs = sum(sum(range(s + 1, s + m + 1)) for s, m in zip(starts, new)) * heads         # (query row, key) pairs
+        k_pages = [torch.randn(sum(blocks) + 1, page, kv_heads, dim, device="cuda").bfloat16() for _ in range(4)]
+        v_pages = [torch.randn(sum(blocks) + 1, page, kv_heads, vdim, device="cuda").bfloat16() for _ in range(4)]
+        q = torch.randn(n, heads * dim, device="cuda").bfloat16()
+        out = torch.empty(n, heads * vdim, device="cuda", dtype=torch.bfloat16)
+        if len(new) == 2:
+            us = replayed_us(torch, lambda i: ops.capped_attention(out, q, k_pages[i % 4], v_pages[i % 4], table, positions, token_item,
+                                                                   heads, kv_heads, dim, vdim, page, 0.125, 50.0, 0, tiled=True))
+            add(f"capped attention in tiles, {name}", us, flops=2.0 * pairs * (dim + vdim), heads=heads, kv_heads=kv_heads, dim=dim)
+        else:
+            chunk, reach = 128, table.shape[1] * page
+            chunks = -(-reach // chunk)
+            scratch = (torch.empty(n * heads * chunks * dim, device="cuda"), torch.empty(n * heads * chunks * 2, device="cuda"),
+                       torch.zeros(n * heads, dtype=torch.int32, device="cuda"))
+            us = replayed_us(torch, lambda i: ops.split_attention(out, q, k_pages[i % 4], v_pages[i % 4], table, positions, token_item,
+                                                                  heads, kv_heads, dim, page, 0.125, 0, chunk, chunks, *scratch, cap=50.0))
+            add(f"capped attention over split keys, {name}", us, bytes_moved=sum(lengths) * kv_heads * (dim + vdim) * 2.0,
+                heads=heads, kv_heads=kv_heads, dim=dim)
+            us = replayed_us(torch, lambda i: ops.capped_attention(out, q, k_pages[i % 4], v_pages[i % 4], table, positions, token_item,
+                                                                   heads, kv_heads, dim, vdim, page, 0.125, 50.0, 0))
+            add(f"capped attention, one block per (token, head), {name}", us, bytes_moved=sum(lengths) * kv_heads * (dim + vdim) * 2.0,
+                heads=heads, kv_heads=kv_heads, dim=dim)
+    # ---- the recurrences ----
+    for kind in ("right", "mamba"):
+        mem = size[kind]
+        delta = kind == "right"
+        h, vd = mem["heads"], mem["vdim"]
+        qk_heads, kd = (mem["kv_heads"], mem["dim"]) if delta else (mem["groups"], mem["state"])
+        for name, counts in (("prompts, 2 x 1024", [1024, 1024]), ("single tokens, 8", [1] * 8)):
+            n = sum(counts)
+            projected = [torch.randn(n, 2 * qk_heads * kd + h * vd, device="cuda").bfloat16() for _ in range(4)]
+            states = [torch.zeros(len(counts), h * kd * vd, device="cuda") for _ in range(4)]
+            out = torch.empty(n, h * vd, device="cuda")
+            gate_a, gate_b = torch.randn(n, h, device="cuda"), torch.randn(n, h, device="cuda")
+            rate, bias, skip = torch.zeros(h, device="cuda"), torch.zeros(h, device="cuda"), torch.ones(h, device="cuda")
+            slots, offs, cnts = dev(list(range(len(counts)))), dev([sum(counts[:i]) for i in range(len(counts))]), dev(counts)
+
+            def launch(i):
+                x = projected[i % 4]
+                ops.linear_recurrence(out, x[:, :qk_heads * kd], x[:, qk_heads * kd:2 * qk_heads * kd], x[:, 2 * qk_heads * kd:], gate_a,
+                                      gate_b if delta else None, rate, bias, states[i % 4], slots, offs, cnts, h, qk_heads, kd, vd,
+                                      delta, unit_norm=delta, q_scale=kd ** -0.5 if delta else 1.0, skip=None if delta else skip)
+            us = replayed_us(torch, launch)
+            label = "gated delta rule" if delta else "state-space recurrence"
+            if len(counts) == 2:
+                # per token and head: two sums over the old state and the state's update, four FMAs an entry
+                add(f"{label}, token by token, {name}", us, flops=2.0 * 4 * kd * vd * h * n, heads=h, dim=kd, vdim=vd)
+            else:
+                add(f"{label}, {name}", us, bytes_moved=2.0 * len(counts) * h * kd * vd * 4, heads=h, dim=kd, vdim=vd)
+    # ---- the routed feed-forward ----
+    moe, width = size["moe"], size["width"]
+    experts, top, inner, shared = moe["experts"], moe["top"], moe["ff"], moe["shared"]
+    total, pairs = experts * inner + shared, top + 1
+    up = [(torch.randn(2 * total, width, device="cuda") * 0.02).bfloat16() for _ in range(4)]
+    down = [(torch.randn(width, total, device="cuda") * 0.02).bfloat16() for _ in range(4)]
+    router, shared_gate = (torch.randn(experts, width, device="cuda") * 0.5).bfloat16(), (torch.randn(1, width, device="cuda") * 0.1).bfloat16()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    starts = [e * inner for e in range(experts)] + [experts * inner]
+    inner_of = dev([inner] * experts + [shared])
+    for name, n in (("2,048 tokens", 2048), ("8 tokens", 8)):
+        x = torch.randn(n, width, device="cuda").bfloat16()
+        hidden = torch.zeros(n, width, device="cuda")
+        choice = torch.zeros(n * pairs, dtype=torch.int32, device="cuda")
+        in_weight, out_weight = torch.zeros(n * pairs, device="cuda"), torch.zeros(n * pairs, device="cuda")
+        us = replayed_us(torch, lambda i: ops.route(x, router, shared_gate, top, choice, in_weight, out_weight))
+        add(f"router, {name}", us, bytes_moved=n * width * 2.0 + experts * width * 2.0, experts=experts, top=top)
+        needed = 2.0 * n * 3 * width * (top * inner + shared)                 # the flops the chosen experts need
+        if n >= 32:
+            gu = torch.empty(n, 2 * total, device="cuda", dtype=torch.bfloat16)
+            act = torch.empty(n, total, device="cuda", dtype=torch.bfloat16)
+
+            def launch(i):
+                ops.gemm_bf16(gu, x, up[i % 4], None, "store", status)
+                ops.expert_combine(act, gu, choice, in_weight, out_weight, experts, inner, top, pairs)
+                ops.gemm_bf16(hidden, act, down[i % 4], None, "add", status)
+            us = replayed_us(torch, launch)
+            add(f"experts, two products over all experts, {name}", us, tensor_flops=needed, executed_tflops=round(2.0 * n * 3 * width * total / us / 1e6, 1),
+                experts=experts, top=top, inner=inner, shared=shared)
+            # the dense feed-forward of equal inner size (the closest model's), the same two products
+            fc = [(torch.randn(size["ff"], width, device="cuda") * 0.02).bfloat16() for _ in range(4)]
+            back = [(torch.randn(width, size["ff"], device="cuda") * 0.02).bfloat16() for _ in range(4)]
+            mid = torch.empty(n, size["ff"], device="cuda", dtype=torch.bfloat16)
+
+            def dense(i):
+                ops.gemm_bf16(mid, x, fc[i % 4], None, "relu_squared", status)
+                ops.gemm_bf16(hidden, mid, back[i % 4], None, "add", status)
+            us = replayed_us(torch, dense)
+            add(f"dense feed-forward of inner {size['ff']}, {name}", us, tensor_flops=2.0 * n * 2 * width * size["ff"])
+        else:
+            act = torch.empty(n * pairs, max(inner, shared), device="cuda", dtype=torch.bfloat16)
+
+            tables = []
+            for i in range(4):
+                size_of = up[i].element_size()
+                tables.append((torch.tensor([up[i].data_ptr() + s_ * width * size_of for s_ in starts], dtype=torch.int64, device="cuda"),
+                               torch.tensor([up[i].data_ptr() + (total + s_) * width * size_of for s_ in starts], dtype=torch.int64, device="cuda"),
+                               torch.tensor([down[i].data_ptr() + s_ * size_of for s_ in starts], dtype=torch.int64, device="cuda")))
+            us = replayed_us(torch, lambda i: ops.experts(hidden, act, x, choice, in_weight, out_weight, *tables[i % 4], inner_of,
+                                                          max(inner, shared), pairs, ld_down=total))
+            # at most every expert once, and the shared one
+            read = min(n * top, experts) * 3 * inner * width * 2.0 + 3 * shared * width * 2.0
+            add(f"experts, pair by pair, {name}", us, bytes_moved=read, experts=experts, top=top, inner=inner, shared=shared)
+    return lines
+
+
+def run_compare_sumozen(args):
+    """Sumozen beside Fuvolix of equal width, depth and inner size: the prompt step of 2,048 tokens
+    (2 x 1,024) and the decode step of ``--batch`` requests at a context of 1,024, in bfloat16,
+    through ``Engine.step``; then the kernels alone, Sumozen's and Fuvolix's.  One JSON line per measurement."""
+    import torch
+    from mini_llm_b200.config import config_from_dict
+    from mini_llm_b200.engine import Engine
+    from mini_llm_b200.weights import write_random_model
+    peak = peaks()
+    context, vocab = 1024, GPT2_SMALL["vocab_size"]
+    for name, size in SUMOZEN_SIZES.items():
+        for design in ("sumozen", "fuvolix"):
+            raw = sumozen_config(size, vocab) if design == "sumozen" else fuvolix_config(FUVOLIX_SIZES[size["fuvolix"]], vocab)
+            with tempfile.TemporaryDirectory() as folder:
+                write_random_model(config_from_dict(raw), 0, folder, recipe="gpt2", store_dtype="bfloat16")
+                engine = Engine(folder, dtype="bfloat16", max_requests=16, cache_tokens=16 * context, max_tokens_per_step=2048,
+                                **({"page_size": args.page_size} if args.page_size else {}))
+                prefill_ms = prefill_run(engine, 2, 1024, vocab)
+                decode_ms, launches, _ = decode_run(engine, args.batch, args.steps, args.warmup, context, vocab)
+                print(json.dumps({"design": design, "size": name, "width": size["width"], "layers": size["layers"], "inner": size["ff"],
+                                  "prefill_2048_tokens_ms": round(prefill_ms, 3), "prefill_tokens_per_s": round(2048 / prefill_ms * 1e3),
+                                  "decode_batch": args.batch, "decode_ms_per_step": round(decode_ms, 3),
+                                  "decode_tokens_per_s": round(args.batch / decode_ms * 1e3), "launches_per_decode_step": launches,
+                                  "weight_bytes": engine.model.weight_bytes, "step_kinds": engine.step_kinds}), flush=True)
+                del engine
+                torch.cuda.empty_cache()
+        for line in sumozen_kernels(torch, size, peak):
+            print(json.dumps(dict(line, design="sumozen", size=name)), flush=True)
+        for line in mixer_kernels(torch, FUVOLIX_SIZES[size["fuvolix"]], peak):
+            print(json.dumps(dict(line, design="fuvolix", size=name)), flush=True)
+    return 0
+
+
 def run_compare(args):
     """Fuvolix beside GPT-2 of equal width, depth and inner size: the prompt step of 2,048 tokens
     (2 x 1,024) and the decode step of ``--batch`` requests at a context of 1,024, in bfloat16,
@@ -934,6 +1139,8 @@ def main():
         return run_reference(args)
     if args.kernels:
         return run_kernels()
+    if args.compare == "sumozen":
+        return run_compare_sumozen(args)
     if args.compare:
         return run_compare(args)
     return run_ours(args)

@@ -192,6 +192,19 @@ constexpr int TILE_ROWS = 16;          // (token, head) rows a block
 constexpr int TILE_WARPS = 8;
 constexpr int TILE_VPL = CAP_MAX_HEAD / 32;
 
+// sixteen bytes of activations as 32-bit floats into shared memory
+template <typename T> __device__ __forceinline__ void widen(const uint4& v, float* dst);
+template <> __device__ __forceinline__ void widen<float>(const uint4& v, float* dst) {
+    *reinterpret_cast<float4*>(dst) = make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
+}
+template <> __device__ __forceinline__ void widen<bf16>(const uint4& v, float* dst) {
+    // a bfloat16 is the upper half of the float it stands for
+    *reinterpret_cast<float4*>(dst) = make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xffff0000u),
+                                                  __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xffff0000u));
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(__uint_as_float(v.z << 16), __uint_as_float(v.z & 0xffff0000u),
+                                                      __uint_as_float(v.w << 16), __uint_as_float(v.w & 0xffff0000u));
+}
+
 template <typename T>
 __global__ void __launch_bounds__(TILE_WARPS * 32)
 capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restrict__ q, long ld_q,
@@ -239,6 +252,39 @@ capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restr
         q_rows[r * dim + d] = to_f32(q[(long)(first_token + r / n_heads_here) * ld_q + (long)(first_head + r % n_heads_here) * dim + d]);
     }
 
+    // A block of 32 keys and values comes in 16-byte vectors, up to MAXV of each per thread; which
+    // (key, column) a thread's vectors are is fixed for the kernel, so no division is left in the loop.
+    constexpr int VEC = 16 / (int)sizeof(T);
+    constexpr int MAXV = TILE_KEYS * CAP_MAX_HEAD / VEC / (TILE_WARPS * 32);
+    uint4 key_vec[MAXV], value_vec[MAXV];
+    int key_row[MAXV], key_col[MAXV], value_row[MAXV], value_col[MAXV];
+#pragma unroll
+    for (int i = 0; i < MAXV; i++) {
+        const int u = threadIdx.x + i * TILE_WARPS * 32;
+        key_row[i] = u < TILE_KEYS * (dim / VEC) ? u / (dim / VEC) : -1;
+        key_col[i] = (u % (dim / VEC)) * VEC;
+        value_row[i] = u < TILE_KEYS * (vdim / VEC) ? u / (vdim / VEC) : -1;
+        value_col[i] = (u % (vdim / VEC)) * VEC;
+        key_vec[i] = value_vec[i] = make_uint4(0, 0, 0, 0);
+    }
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1;
+    auto fetch = [&](const int* bt, int base, int p_last) {
+#pragma unroll
+        for (int i = 0; i < MAXV; i++) {
+            const int kp = base + key_row[i], vp = base + value_row[i];
+            if (key_row[i] >= 0 && kp <= p_last) {
+                const int block = page_shift >= 0 ? kp >> page_shift : kp / page_size;
+                const long slot = (long)bt[block] * page_size + (kp - block * page_size);
+                key_vec[i] = *reinterpret_cast<const uint4*>(k_pages + (slot * n_kv_heads + hk) * dim + key_col[i]);
+            }
+            if (value_row[i] >= 0 && vp <= p_last) {
+                const int block = page_shift >= 0 ? vp >> page_shift : vp / page_size;
+                const long slot = (long)bt[block] * page_size + (vp - block * page_size);
+                value_vec[i] = *reinterpret_cast<const uint4*>(v_pages + (slot * n_kv_heads + hk) * vdim + value_col[i]);
+            }
+        }
+    };
+
     int run_first = 0;
     while (run_first < n_tok) {
         // a run: consecutive tokens of the tile that belong to one request
@@ -248,20 +294,19 @@ capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restr
         const int p_first = positions[first_token + run_first], p_last = positions[first_token + run_last];
         const int lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
         const int* bt = block_table + (long)item * max_blocks;
-        for (int base = (lo / TILE_KEYS) * TILE_KEYS; base <= p_last; base += TILE_KEYS) {
+        const int first_base = (lo / TILE_KEYS) * TILE_KEYS;
+        fetch(bt, first_base, p_last);
+        for (int base = first_base; base <= p_last; base += TILE_KEYS) {
             __syncthreads();                                  // the block before has been read; q_rows are written
             const int n_keys = min(TILE_KEYS, p_last + 1 - base);
-            for (int u = threadIdx.x; u < n_keys * dim; u += blockDim.x) {
-                const int j = u / dim, d = u % dim, pos = base + j;
-                const long slot = (long)bt[pos / page_size] * page_size + (pos % page_size);
-                keys[j * kd + d] = to_f32(k_pages[(slot * n_kv_heads + hk) * dim + d]);
-            }
-            for (int u = threadIdx.x; u < n_keys * vdim; u += blockDim.x) {
-                const int j = u / vdim, d = u % vdim, pos = base + j;
-                const long slot = (long)bt[pos / page_size] * page_size + (pos % page_size);
-                values[j * vdim + d] = to_f32(v_pages[(slot * n_kv_heads + hk) * vdim + d]);
+#pragma unroll
+            for (int i = 0; i < MAXV; i++) {
+                if (key_row[i] >= 0 && key_row[i] < n_keys) widen<T>(key_vec[i], keys + key_row[i] * kd + key_col[i]);
+                if (value_row[i] >= 0 && value_row[i] < n_keys) widen<T>(value_vec[i], values + value_row[i] * vdim + value_col[i]);
             }
             __syncthreads();
+            // the next block's rows are asked for now and arrive while this one is worked on
+            if (base + TILE_KEYS <= p_last) fetch(bt, base + TILE_KEYS, p_last);
             bool any = false;
             float score[2];
 #pragma unroll
@@ -340,8 +385,10 @@ static size_t capped_tiled_shared(int dim, int vdim) {
     return sizeof(float) * ((size_t)TILE_ROWS * dim + (size_t)TILE_KEYS * (dim + 4) + (size_t)TILE_KEYS * vdim + TILE_WARPS * 2 * TILE_KEYS);
 }
 
-extern "C" int mllm_hybrid_capped_attention_tiled_takes(int dim, int vdim) {
-    return dim > 0 && vdim > 0 && dim % 4 == 0 && vdim <= CAP_MAX_HEAD && capped_tiled_shared(dim, vdim) <= 160 * 1024;
+// (keys and values in whole 16-byte vectors: sizes that are multiples of `vec` elements)
+extern "C" int mllm_hybrid_capped_attention_tiled_takes(int dim, int vdim, int vec) {
+    return dim > 0 && vdim > 0 && dim % vec == 0 && vdim % vec == 0 && dim % 4 == 0 && vdim % 4 == 0 && dim <= CAP_MAX_HEAD &&
+           vdim <= CAP_MAX_HEAD && capped_tiled_shared(dim, vdim) <= 160 * 1024;
 }
 
 template <typename T>
@@ -377,7 +424,7 @@ extern "C" int mllm_hybrid_capped_attention(void* out, long ld_out, const void* 
     if (dim <= 0 || dim > CAP_MAX_HEAD || vdim <= 0 || vdim > CAP_MAX_HEAD) return fail("capped_attention: key and value sizes must be in 1..256");
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return fail("capped_attention: heads must be a multiple of the key/value heads");
     if (n_heads > 65535) return fail("capped_attention: too many heads for one launch");
-    if (tiled && !mllm_hybrid_capped_attention_tiled_takes(dim, vdim)) return fail("capped_attention: the tiles do not take these sizes");
+    if (tiled && !mllm_hybrid_capped_attention_tiled_takes(dim, vdim, dtype == DT_F32 ? 4 : 8)) return fail("capped_attention: the tiles do not take these sizes");
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == DT_F32)
         return launch_capped_attention<float>(tiled != 0, out, ld_out, q, ld_q, k_pages, v_pages, block_table, max_blocks, positions,
@@ -399,7 +446,8 @@ extern "C" int mllm_hybrid_capped_attention(void* out, long ld_out, const void* 
 // One block per (entry, head, slice of the value entries): a column of S belongs to LANES threads
 // of one warp, each with DPT rows in registers; both sums over the old column (with k and with q)
 // are taken in one pass, and the read-out follows from them: S_new^T q = a S^T q + u (k . q).
-// The entry's tokens are taken in order, TOK at a time through shared memory.
+// The entry's tokens are taken in order, TOK at a time through shared memory; a chunk's rows are
+// asked for into registers while the chunk before it is worked on.
 // ---------------------------------------------------------------------------
 struct RecurrenceParams {
     float* out; long ld_out;
@@ -418,13 +466,16 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
     dependents_may_start();
     wait_for_earlier_kernels();
     constexpr int COLS = 128 / LANES;
+    constexpr int TPR = 128 / (2 * TOK);                   // threads that bring one staged row (k or q of a token)
+    constexpr int PER = (DPT * LANES + TPR - 1) / TPR;     // entries of that row a thread brings
+    constexpr int VPER = (TOK * COLS + 127) / 128;         // values a thread brings
     extern __shared__ float shared[];
     const int dim = pp.dim, vdim = pp.vdim;
     float* ks = shared;                         // [TOK][dim]
     float* qs = ks + TOK * dim;                 // [TOK][dim]
     float* vs = qs + TOK * dim;                 // [TOK][COLS]
-    float* as = vs + TOK * COLS;                // [TOK] decay
-    float* bs = as + TOK;                       // [TOK] write strength
+    float* as = vs + TOK * COLS;                // [TOK] the step's gate, then the decay
+    float* bs = as + TOK;                       // [TOK] the write gate, then the write strength
     float* kq = bs + TOK;                       // [TOK] k . q
     const int item = blockIdx.x, head = blockIdx.y;
     const int count = pp.item_count[item];
@@ -448,26 +499,64 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
     const T* k = (const T*)pp.k;
     const T* v = (const T*)pp.v;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // What a thread brings of every chunk of TOK tokens: PER entries of one row (the k or the q of one
+    // token), VPER values, and (the first threads) a token's gates.  The next chunk is asked for
+    // before the current one is worked on, so its way through the memory lies under the sums.
+    const int row = threadIdx.x / TPR, row_sub = threadIdx.x % TPR;
+    const int row_token = row >> 1;
+    const T* row_base = (row & 1) ? q : k;
+    const long row_ld = (row & 1) ? pp.ld_q : pp.ld_k;
+    float* row_smem = ((row & 1) ? qs : ks) + row_token * dim;
+    T raw[PER], raw_v[VPER];
+    float raw_a = 0.0f, raw_b = 0.0f;
+    auto ask = [&](int start) {
+        const int n = min(TOK, count - start);
+        const long t0 = first + start;
+#pragma unroll
+        for (int i = 0; i < PER; i++) {
+            const int d = row_sub + TPR * i;
+            raw[i] = (row_token < n && d < dim) ? row_base[(t0 + row_token) * row_ld + (long)qk_head * dim + d] : from_f32<T>(0.0f);
+        }
+#pragma unroll
+        for (int i = 0; i < VPER; i++) {
+            const int u = threadIdx.x + 128 * i, tt = u / COLS, c = blockIdx.z * COLS + u % COLS;
+            raw_v[i] = (tt < n && c < vdim) ? v[(t0 + tt) * pp.ld_v + (long)head * vdim + c] : from_f32<T>(0.0f);
+        }
+        if (threadIdx.x < n) {
+            raw_a = pp.gate_a[(t0 + threadIdx.x) * pp.ld_gate_a + head];
+            if (pp.delta) raw_b = pp.gate_b[(t0 + threadIdx.x) * pp.ld_gate_b + head];
+        }
+    };
+    ask(0);
     for (int start = 0; start < count; start += TOK) {
         const int n = min(TOK, count - start);
+        __syncthreads();                                      // the chunk before has been read
+#pragma unroll
+        for (int i = 0; i < PER; i++) {
+            const int d = row_sub + TPR * i;
+            if (d < dim) row_smem[d] = to_f32(raw[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < VPER; i++) {
+            const int u = threadIdx.x + 128 * i;
+            if (u < TOK * COLS) vs[u] = to_f32(raw_v[i]);
+        }
+        if (threadIdx.x < TOK) as[threadIdx.x] = raw_a, bs[threadIdx.x] = raw_b;
         __syncthreads();
-        // a warp stages a token: k and q of the head (unit vectors if asked), their product, the gates
+        // a warp finishes a token: unit vectors if asked, k . q, the step, the decay, the write strength
         for (int tt = warp; tt < n; tt += 4) {
-            const long t = first + start + tt;
-            float sk = 0.0f, sq = 0.0f;
-            for (int d = lane; d < dim; d += 32) {
-                const float kv = to_f32(k[t * pp.ld_k + (long)qk_head * dim + d]);
-                const float qv = to_f32(q[t * pp.ld_q + (long)qk_head * dim + d]);
-                ks[tt * dim + d] = kv, qs[tt * dim + d] = qv;
-                sk = fmaf(kv, kv, sk), sq = fmaf(qv, qv, sq);
-            }
             float fk = 1.0f, fq = pp.q_scale;
             if (pp.unit_norm) {
+                float sk = 0.0f, sq = 0.0f;
+                for (int d = lane; d < dim; d += 32) {
+                    const float kv = ks[tt * dim + d], qv = qs[tt * dim + d];
+                    sk = fmaf(kv, kv, sk), sq = fmaf(qv, qv, sq);
+                }
                 fk = 1.0f / sqrtf(warp_sum(sk) + 1e-6f);
                 fq = pp.q_scale / sqrtf(warp_sum(sq) + 1e-6f);
             }
             float dot = 0.0f;
-            __syncwarp();
             for (int d = lane; d < dim; d += 32) {
                 const float kv = ks[tt * dim + d] * fk, qv = qs[tt * dim + d] * fq;
                 ks[tt * dim + d] = kv, qs[tt * dim + d] = qv;
@@ -475,40 +564,39 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
             }
             dot = warp_sum(dot);
             if (lane == 0) {
-                const float step = softplus_f(pp.gate_a[t * pp.ld_gate_a + head] + bias);
+                const float step = softplus_f(as[tt] + bias);
+                const float write = pp.delta ? sigmoid_f(bs[tt]) : step;
                 as[tt] = expf(-rate * step);
-                bs[tt] = pp.delta ? sigmoid_f(pp.gate_b[t * pp.ld_gate_b + head]) : step;
+                bs[tt] = write;
                 kq[tt] = dot;
             }
         }
-        for (int u = threadIdx.x; u < n * COLS; u += blockDim.x) {
-            const int tt = u / COLS, c = blockIdx.z * COLS + u % COLS;
-            vs[u] = c < vdim ? to_f32(v[(first + start + tt) * pp.ld_v + (long)head * vdim + c]) : 0.0f;
-        }
         __syncthreads();
+        if (start + TOK < count) ask(start + TOK);
         for (int tt = 0; tt < n; tt++) {
             const float* kr = ks + tt * dim;
             const float* qr = qs + tt * dim;
-            float dk = 0.0f, dq = 0.0f;
+            float dk[2] = {0.0f, 0.0f}, dq[2] = {0.0f, 0.0f};      // two chains each: half the latency
 #pragma unroll
             for (int r = 0; r < DPT; r++) {
                 const int i = lane_in + LANES * r;
-                if (i < dim) dk = fmaf(s[r], kr[i], dk), dq = fmaf(s[r], qr[i], dq);
+                if (i < dim) dk[r & 1] = fmaf(s[r], kr[i], dk[r & 1]), dq[r & 1] = fmaf(s[r], qr[i], dq[r & 1]);
             }
+            float sum_k = dk[0] + dk[1], sum_q = dq[0] + dq[1];
 #pragma unroll
             for (int o = LANES / 2; o > 0; o >>= 1) {
-                dk += __shfl_xor_sync(0xffffffffu, dk, o);
-                dq += __shfl_xor_sync(0xffffffffu, dq, o);
+                sum_k += __shfl_xor_sync(0xffffffffu, sum_k, o);
+                sum_q += __shfl_xor_sync(0xffffffffu, sum_q, o);
             }
             const float a = as[tt], b = bs[tt], value = vs[tt * COLS + col_local];
-            const float u = pp.delta ? b * (value - a * dk) : b * value;
+            const float u = pp.delta ? b * (value - a * sum_k) : b * value;
 #pragma unroll
             for (int r = 0; r < DPT; r++) {
                 const int i = lane_in + LANES * r;
                 if (i < dim) s[r] = fmaf(kr[i], u, a * s[r]);
             }
             if (live && lane_in == 0)
-                pp.out[(first + start + tt) * pp.ld_out + (long)head * vdim + col] = fmaf(u, kq[tt], a * dq) + skip * value;
+                pp.out[(first + start + tt) * pp.ld_out + (long)head * vdim + col] = fmaf(u, kq[tt], a * sum_q) + skip * value;
         }
     }
     if (pp.writes && live) {
@@ -529,11 +617,13 @@ static int launch_recurrence(const RecurrenceParams& pp, int n_items, cudaStream
     return check_launch("linear_recurrence_kernel");
 }
 
+// A column of the state over 4 lanes for small keys, over 8 from 33 entries on (shorter sums, more
+// blocks for the same state), over a whole warp past 256.
 template <typename T>
 static int pick_recurrence(const RecurrenceParams& pp, int n_items, cudaStream_t s) {
     if (pp.dim <= 32) return launch_recurrence<T, 8, 4, 16>(pp, n_items, s);
-    if (pp.dim <= 64) return launch_recurrence<T, 16, 4, 16>(pp, n_items, s);
-    if (pp.dim <= 128) return launch_recurrence<T, 32, 4, 16>(pp, n_items, s);
+    if (pp.dim <= 64) return launch_recurrence<T, 8, 8, 16>(pp, n_items, s);
+    if (pp.dim <= 128) return launch_recurrence<T, 16, 8, 16>(pp, n_items, s);
     if (pp.dim <= 256) return launch_recurrence<T, 32, 8, 16>(pp, n_items, s);
     return launch_recurrence<T, 32, 32, 4>(pp, n_items, s);
 }
@@ -570,6 +660,27 @@ extern "C" int mllm_hybrid_linear_recurrence(const RecurrenceParams* params, int
 //   expert_combine   act[t, c] = silu(s G[t, c]) * (s U[t, c]) * out_weight for column c of expert e,
 //                    s = the token's input weight for e, or 0
 // ---------------------------------------------------------------------------
+// Sixteen bytes of a row as 32-bit floats in registers: 8 bfloat16 or 4 floats.
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float* out) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        out[0] = v.x, out[1] = v.y, out[2] = v.z, out[3] = v.w;
+    }
+};
+template <> struct Vec16<bf16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const bf16* p, float* out) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        out[0] = __uint_as_float(v.x << 16), out[1] = __uint_as_float(v.x & 0xffff0000u);
+        out[2] = __uint_as_float(v.y << 16), out[3] = __uint_as_float(v.y & 0xffff0000u);
+        out[4] = __uint_as_float(v.z << 16), out[5] = __uint_as_float(v.z & 0xffff0000u);
+        out[6] = __uint_as_float(v.w << 16), out[7] = __uint_as_float(v.w & 0xffff0000u);
+    }
+};
+__device__ __forceinline__ bool aligned16(const void* p) { return (reinterpret_cast<unsigned long long>(p) & 15ull) == 0; }
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 route_kernel(const T* __restrict__ x, long ld_x, const T* __restrict__ router, const T* __restrict__ shared_gate, int width,
@@ -637,9 +748,20 @@ expert_up_kernel(T* __restrict__ act, long ld_act, const T* __restrict__ x, long
         const T* g = gate + (long)f * width;
         const T* u = up + (long)f * width;
         float zg = 0.0f, zu = 0.0f;
-        for (int c = lane; c < width; c += 32) {
-            zg = fmaf(to_f32(g[c]), row[c], zg);
-            zu = fmaf(to_f32(u[c]), row[c], zu);
+        constexpr int N = Vec16<T>::N;
+        if (width % N == 0 && aligned16(g) && aligned16(u)) {
+            for (int c = lane * N; c < width; c += 32 * N) {
+                float a[N], b[N];
+                Vec16<T>::load(g + c, a);
+                Vec16<T>::load(u + c, b);
+#pragma unroll
+                for (int i = 0; i < N; i++) zg = fmaf(a[i], row[c + i], zg), zu = fmaf(b[i], row[c + i], zu);
+            }
+        } else {
+            for (int c = lane; c < width; c += 32) {
+                zg = fmaf(to_f32(g[c]), row[c], zg);
+                zu = fmaf(to_f32(u[c]), row[c], zu);
+            }
         }
         zg = warp_sum(zg), zu = warp_sum(zu);
         if (lane == 0) act[(long)pair * ld_act + f] = from_f32<T>(silu_f(zg) * zu);
@@ -663,7 +785,18 @@ expert_down_kernel(float* __restrict__ hidden, long ld_hidden, const T* __restri
             const T* w = (const T*)down_of[e] + (long)c * ld_down;
             const T* a = act + pair * ld_act;
             float z = 0.0f;
-            for (int f = lane; f < inner; f += 32) z = fmaf(to_f32(w[f]), to_f32(a[f]), z);
+            constexpr int N = Vec16<T>::N;
+            if (inner % N == 0 && aligned16(w) && aligned16(a)) {
+                for (int f = lane * N; f < inner; f += 32 * N) {
+                    float x[N], y[N];
+                    Vec16<T>::load(w + f, x);
+                    Vec16<T>::load(a + f, y);
+#pragma unroll
+                    for (int i = 0; i < N; i++) z = fmaf(x[i], y[i], z);
+                }
+            } else {
+                for (int f = lane; f < inner; f += 32) z = fmaf(to_f32(w[f]), to_f32(a[f]), z);
+            }
             total = fmaf(out_weight[pair], warp_sum(z), total);
         }
         if (lane == 0) hidden[(long)t * ld_hidden + c] += total;

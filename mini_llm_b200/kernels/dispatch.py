@@ -137,7 +137,7 @@ class Kernels:
             return ops.split_attention(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions, ctx.token_item,
                                        n_heads, n_kv_heads, dim, cache.page_size, scale, window, chunk, -(-reach // chunk), acc,
                                        ml, counters, cap=cap)
-        tiled = not ctx.decode_only and ops.capped_attention_tiled_takes(dim, vdim)
+        tiled = not ctx.decode_only and ops.capped_attention_tiled_takes(dim, vdim, q.dtype)
         self.chose("capped_attention", "capped_attention_tiled" if tiled else "capped_attention_plain", q.shape[0], n_heads, dim, vdim)
         return ops.capped_attention(out, q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions, ctx.token_item,
                                     n_heads, n_kv_heads, dim, vdim, cache.page_size, scale, cap, window, tiled)

@@ -1179,10 +1179,12 @@ _capped_attention = Function("hybrid", "mllm_hybrid_capped_attention",
                              [P, L, P, L, P, P, P, I, P, P, I, I, I, I, I, I, F, F, I, I, I, P])
 
 
-def capped_attention_tiled_takes(dim, vdim) -> bool:
-    """Whether the tiled kernel takes the sizes: a block's queries, 32 keys and 32 values lie in
-    shared memory in 32-bit (the launcher's own arithmetic)."""
-    return (0 < dim <= 256 and 0 < vdim <= 256 and dim % 4 == 0
+def capped_attention_tiled_takes(dim, vdim, dtype=torch.bfloat16) -> bool:
+    """Whether the tiled kernel takes the sizes: keys and values come in whole 16-byte vectors, and
+    a block's queries, 32 keys and 32 values lie in shared memory in 32-bit (the launcher's own
+    arithmetic)."""
+    vec = 4 if dtype == torch.float32 else 8
+    return (0 < dim <= 256 and 0 < vdim <= 256 and dim % vec == 0 and vdim % vec == 0
             and 4 * (16 * dim + 32 * (dim + 4) + 32 * vdim + 512) <= 160 * 1024)
 
 
