@@ -179,18 +179,18 @@ capped_attention_plain_kernel(T* __restrict__ out, long ld_out, const T* __restr
 }
 
 // ---------------------------------------------------------------------------
-// The same attention in tiles, for steps with prompt portions.  A block takes ROWS consecutive
-// tokens of the step and HC query heads of one key/value head: up to 16 (token, head) rows, two
-// a warp.  Tokens of one request that lie side by side share every block of 32 cached keys and
-// values, which the block brings into shared memory once, in 32-bit.  Within a warp the lanes take
-// the 32 keys of a block for the scores, and the value entries for the weighted sum; scores,
-// maxima, sums and weights are 32-bit.  A tile whose tokens belong to several requests takes the
-// requests one after the other.
+// The same attention in tiles, for steps with prompt portions.  A block takes consecutive tokens
+// of the step and up to HC query heads of one key/value head: 8 * R (token, head) rows, R a warp
+// (R = 2, 4 or 8: the more rows a step has, the more of them share a block's keys).  Tokens of
+// one request that lie side by side share every block of 32 cached keys and values, which the
+// block brings into shared memory once, in 32-bit, as 16-byte vectors asked for a block ahead.
+// Within a warp the lanes take the 32 keys of a block for the scores (a key's entries are read
+// once for all R rows) and the value entries for the weighted sum (a value's entry is read once
+// for all R rows); scores, maxima, sums and weights are 32-bit.  A tile whose tokens belong to
+// several requests takes the requests one after the other.
 // ---------------------------------------------------------------------------
 constexpr int TILE_KEYS = 32;
-constexpr int TILE_ROWS = 16;          // (token, head) rows a block
 constexpr int TILE_WARPS = 8;
-constexpr int TILE_VPL = CAP_MAX_HEAD / 32;
 
 // sixteen bytes of activations as 32-bit floats into shared memory
 template <typename T> __device__ __forceinline__ void widen(const uint4& v, float* dst);
@@ -205,7 +205,7 @@ template <> __device__ __forceinline__ void widen<bf16>(const uint4& v, float* d
                                                       __uint_as_float(v.w << 16), __uint_as_float(v.w & 0xffff0000u));
 }
 
-template <typename T>
+template <typename T, int R, int VPL>       // rows a warp; value entries a lane (vdim <= 32 * VPL)
 __global__ void __launch_bounds__(TILE_WARPS * 32)
 capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restrict__ q, long ld_q,
                               const T* __restrict__ k_pages, const T* __restrict__ v_pages,
@@ -215,12 +215,13 @@ capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restr
                               int heads_per_block) {
     dependents_may_start();
     wait_for_earlier_kernels();
+    constexpr int ROWS = TILE_WARPS * R;
     extern __shared__ float shared[];
     const int kd = dim + 4;                                  // padded key row: lanes read rows, four entries at a time
-    float* q_rows = shared;                                  // [TILE_ROWS][dim]
-    float* keys = q_rows + TILE_ROWS * dim;                  // [TILE_KEYS][kd]
+    float* q_rows = shared;                                  // [ROWS][dim]
+    float* keys = q_rows + ROWS * dim;                       // [TILE_KEYS][kd]
     float* values = keys + TILE_KEYS * kd;                   // [TILE_KEYS][vdim]
-    float* weights = values + TILE_KEYS * vdim;              // [TILE_WARPS][2][TILE_KEYS]
+    float* weights = values + TILE_KEYS * vdim;              // [TILE_WARPS][TILE_KEYS][R]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int group = n_heads / n_kv_heads;
     const int chunks = (group + heads_per_block - 1) / heads_per_block;
@@ -232,20 +233,19 @@ capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restr
     const int n_rows = n_tok * n_heads_here;
     const float inv_cap = cap > 0.0f ? 1.0f / cap : 0.0f;
 
-    // this warp's two rows: r = warp and warp + TILE_WARPS; row r = (token r / heads, head r % heads)
-    int row_token[2], row_head[2], row_pos[2], row_item[2];
-    float m[2], l[2], acc[2][TILE_VPL];
+    // this warp's rows: r = warp + s * TILE_WARPS; row r = (token r / heads, head r % heads)
+    int row_pos[R], row_item[R];
+    float m[R], l[R], acc[R][VPL];
 #pragma unroll
-    for (int s = 0; s < 2; s++) {
+    for (int s = 0; s < R; s++) {
         const int r = warp + s * TILE_WARPS;
         const bool live = r < n_rows;
-        row_token[s] = live ? first_token + r / n_heads_here : -1;
-        row_head[s] = live ? first_head + r % n_heads_here : 0;
-        row_pos[s] = live ? positions[row_token[s]] : -1;
-        row_item[s] = live ? token_item[row_token[s]] : -1;
+        const int token = live ? first_token + r / n_heads_here : 0;
+        row_pos[s] = live ? positions[token] : -1;
+        row_item[s] = live ? token_item[token] : -1;
         m[s] = -INFINITY, l[s] = 0.0f;
 #pragma unroll
-        for (int i = 0; i < TILE_VPL; i++) acc[s][i] = 0.0f;
+        for (int i = 0; i < VPL; i++) acc[s][i] = 0.0f;
     }
     for (int u = threadIdx.x; u < n_rows * dim; u += blockDim.x) {
         const int r = u / dim, d = u % dim;
@@ -285,6 +285,7 @@ capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restr
         }
     };
 
+    float* my_weights = weights + warp * TILE_KEYS * R;
     int run_first = 0;
     while (run_first < n_tok) {
         // a run: consecutive tokens of the tile that belong to one request
@@ -307,61 +308,66 @@ capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restr
             __syncthreads();
             // the next block's rows are asked for now and arrive while this one is worked on
             if (base + TILE_KEYS <= p_last) fetch(bt, base + TILE_KEYS, p_last);
-            bool any = false;
-            float score[2];
+            // which of the warp's rows see a key of this block at all
+            bool any = false, seen[R];
+            int first_seen[R];
 #pragma unroll
-            for (int s = 0; s < 2; s++) {
-                score[s] = -INFINITY;
-                const int pos = base + lane;
-                const int first_seen = (window > 0 && row_pos[s] - window + 1 > 0) ? row_pos[s] - window + 1 : 0;
-                const bool mine = row_item[s] == item;
-                if (mine && base <= row_pos[s] && base + TILE_KEYS > first_seen) any = true;
-                if (mine && lane < n_keys && pos <= row_pos[s] && pos >= first_seen) {
-                    const float* qr = q_rows + (warp + s * TILE_WARPS) * dim;
-                    const float* kr = keys + lane * kd;
-                    float dot = 0.0f;
-                    int d = 0;
-                    for (; d + 4 <= dim; d += 4) {
-                        const float4 a = *reinterpret_cast<const float4*>(qr + d);
-                        const float4 b = *reinterpret_cast<const float4*>(kr + d);
-                        dot = fmaf(a.x, b.x, dot);
-                        dot = fmaf(a.y, b.y, dot);
-                        dot = fmaf(a.z, b.z, dot);
-                        dot = fmaf(a.w, b.w, dot);
-                    }
-                    for (; d < dim; d++) dot = fmaf(qr[d], kr[d], dot);
-                    score[s] = capped(dot * scale, cap, inv_cap);
-                }
+            for (int s = 0; s < R; s++) {
+                first_seen[s] = (window > 0 && row_pos[s] - window + 1 > 0) ? row_pos[s] - window + 1 : 0;
+                seen[s] = row_item[s] == item && base <= row_pos[s] && base + TILE_KEYS > first_seen[s];
+                any = any || seen[s];
             }
             if (!any) continue;                               // (uniform in the warp; the barriers are at the loop's head)
+            // scores: this lane's key against the warp's rows, four entries at a time
+            float dot[R];
 #pragma unroll
-            for (int s = 0; s < 2; s++) {
-                const float block_max = warp_max(score[s]);
+            for (int s = 0; s < R; s++) dot[s] = 0.0f;
+            const float* kr = keys + lane * kd;
+            for (int d = 0; d < dim; d += 4) {
+                const float4 b = *reinterpret_cast<const float4*>(kr + d);
+#pragma unroll
+                for (int s = 0; s < R; s++) {
+                    const float4 a = *reinterpret_cast<const float4*>(q_rows + (warp + s * TILE_WARPS) * dim + d);
+                    dot[s] = fmaf(a.x, b.x, dot[s]);
+                    dot[s] = fmaf(a.y, b.y, dot[s]);
+                    dot[s] = fmaf(a.z, b.z, dot[s]);
+                    dot[s] = fmaf(a.w, b.w, dot[s]);
+                }
+            }
+            const int pos = base + lane;
+#pragma unroll
+            for (int s = 0; s < R; s++) {
+                const bool mine = seen[s] && lane < n_keys && pos <= row_pos[s] && pos >= first_seen[s];
+                const float score = mine ? capped(dot[s] * scale, cap, inv_cap) : -INFINITY;
+                const float block_max = warp_max(score);
                 float rescale = 1.0f, e = 0.0f;
                 if (block_max != -INFINITY) {
                     const float m_new = fmaxf(m[s], block_max);
                     rescale = expf(m[s] - m_new);
-                    e = score[s] == -INFINITY ? 0.0f : expf(score[s] - m_new);
+                    e = mine ? expf(score - m_new) : 0.0f;
                     m[s] = m_new;
                 }
                 l[s] = l[s] * rescale + warp_sum(e);
 #pragma unroll
-                for (int i = 0; i < TILE_VPL; i++) acc[s][i] *= rescale;
-                weights[(warp * 2 + s) * TILE_KEYS + lane] = e;
+                for (int i = 0; i < VPL; i++) acc[s][i] *= rescale;
+                my_weights[lane * R + s] = e;
             }
             __syncwarp();
-            const float* w0 = weights + (warp * 2) * TILE_KEYS;
-            const float* w1 = w0 + TILE_KEYS;
             for (int j = 0; j < n_keys; j++) {
-                const float a = w0[j], b = w1[j];
+                float w[R];
+#pragma unroll
+                for (int s = 0; s < R; s += 2) {
+                    const float2 pair = *reinterpret_cast<const float2*>(my_weights + j * R + s);
+                    w[s] = pair.x, w[s + 1] = pair.y;
+                }
                 const float* vr = values + j * vdim;
 #pragma unroll
-                for (int i = 0; i < TILE_VPL; i++) {
+                for (int i = 0; i < VPL; i++) {
                     const int d = lane + 32 * i;
-                    if (d < vdim) {
-                        const float v = vr[d];
-                        acc[0][i] = fmaf(a, v, acc[0][i]);
-                        acc[1][i] = fmaf(b, v, acc[1][i]);
+                    if (i + 1 < VPL || d < vdim) {
+                        const float v = d < vdim ? vr[d] : 0.0f;
+#pragma unroll
+                        for (int s = 0; s < R; s++) acc[s][i] = fmaf(w[s], v, acc[s][i]);
                     }
                 }
             }
@@ -370,25 +376,48 @@ capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restr
         run_first = run_last + 1;
     }
 #pragma unroll
-    for (int s = 0; s < 2; s++) {
-        if (row_token[s] < 0) continue;
+    for (int s = 0; s < R; s++) {
+        const int r = warp + s * TILE_WARPS;
+        if (r >= n_rows) continue;
+        const int token = first_token + r / n_heads_here, head = first_head + r % n_heads_here;
         const float inv = 1.0f / l[s];
 #pragma unroll
-        for (int i = 0; i < TILE_VPL; i++) {
+        for (int i = 0; i < VPL; i++) {
             const int d = lane + 32 * i;
-            if (d < vdim) out[(long)row_token[s] * ld_out + (long)row_head[s] * vdim + d] = from_f32<T>(acc[s][i] * inv);
+            if (d < vdim) out[(long)token * ld_out + (long)head * vdim + d] = from_f32<T>(acc[s][i] * inv);
         }
     }
 }
 
-static size_t capped_tiled_shared(int dim, int vdim) {
-    return sizeof(float) * ((size_t)TILE_ROWS * dim + (size_t)TILE_KEYS * (dim + 4) + (size_t)TILE_KEYS * vdim + TILE_WARPS * 2 * TILE_KEYS);
+static size_t capped_tiled_shared(int dim, int vdim, int rows_per_warp) {
+    return sizeof(float) * ((size_t)TILE_WARPS * rows_per_warp * dim + (size_t)TILE_KEYS * (dim + 4) + (size_t)TILE_KEYS * vdim +
+                            (size_t)TILE_WARPS * TILE_KEYS * rows_per_warp);
 }
 
 // (keys and values in whole 16-byte vectors: sizes that are multiples of `vec` elements)
 extern "C" int mllm_hybrid_capped_attention_tiled_takes(int dim, int vdim, int vec) {
     return dim > 0 && vdim > 0 && dim % vec == 0 && vdim % vec == 0 && dim % 4 == 0 && vdim % 4 == 0 && dim <= CAP_MAX_HEAD &&
-           vdim <= CAP_MAX_HEAD && capped_tiled_shared(dim, vdim) <= 160 * 1024;
+           vdim <= CAP_MAX_HEAD && capped_tiled_shared(dim, vdim, 2) <= 160 * 1024;
+}
+
+template <typename T, int R, int VPL>
+static int launch_capped_tiles(void* out, long ld_out, const void* q, long ld_q, const void* k_pages, const void* v_pages,
+                               const int* block_table, int max_blocks, const int* positions, const int* token_item, int n_tokens,
+                               int n_heads, int n_kv_heads, int dim, int vdim, int page_size, float scale, float cap, int window,
+                               cudaStream_t s) {
+    constexpr int ROWS = TILE_WARPS * R;
+    const int group = n_heads / n_kv_heads;
+    const int heads_per_block = group < ROWS ? group : ROWS;
+    const int tokens_per_block = ROWS / heads_per_block;
+    const int chunks = (group + heads_per_block - 1) / heads_per_block;
+    const size_t shared = capped_tiled_shared(dim, vdim, R);
+    cudaError_t e = cudaFuncSetAttribute(capped_attention_tiled_kernel<T, R, VPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    if (e != cudaSuccess) return fail("capped_attention: the tiles' shared memory was refused");
+    dim3 grid((n_tokens + tokens_per_block - 1) / tokens_per_block, n_kv_heads * chunks);
+    launch_kernel(g_dependent_launch != 0, capped_attention_tiled_kernel<T, R, VPL>, grid, dim3(TILE_WARPS * 32), shared, s, (T*)out,
+                  ld_out, (const T*)q, ld_q, (const T*)k_pages, (const T*)v_pages, block_table, max_blocks, positions, token_item,
+                  n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, tokens_per_block, heads_per_block);
+    return check_launch("capped_attention_tiled_kernel");
 }
 
 template <typename T>
@@ -402,18 +431,21 @@ static int launch_capped_attention(bool tiled, void* out, long ld_out, const voi
                       token_item, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window);
         return check_launch("capped_attention_plain_kernel");
     }
-    const int group = n_heads / n_kv_heads;
-    const int heads_per_block = group < TILE_ROWS ? group : TILE_ROWS;
-    const int tokens_per_block = TILE_ROWS / heads_per_block;
-    const int chunks = (group + heads_per_block - 1) / heads_per_block;
-    const size_t shared = capped_tiled_shared(dim, vdim);
-    cudaError_t e = cudaFuncSetAttribute(capped_attention_tiled_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-    if (e != cudaSuccess) return fail("capped_attention: the tiles' shared memory was refused");
-    dim3 grid((n_tokens + tokens_per_block - 1) / tokens_per_block, n_kv_heads * chunks);
-    launch_kernel(g_dependent_launch != 0, capped_attention_tiled_kernel<T>, grid, dim3(TILE_WARPS * 32), shared, s, (T*)out, ld_out,
-                  (const T*)q, ld_q, (const T*)k_pages, (const T*)v_pages, block_table, max_blocks, positions, token_item,
-                  n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, tokens_per_block, heads_per_block);
-    return check_launch("capped_attention_tiled_kernel");
+    // rows a warp: the more (token, head) rows a step has, the more of them share a block's keys,
+    // as long as the blocks still fill the GPU and their shared memory fits
+    const long rows = (long)n_tokens * n_heads;
+    int per_warp = rows >= 16384 ? 8 : (rows >= 8192 ? 4 : 2);
+    while (per_warp > 2 && capped_tiled_shared(dim, vdim, per_warp) > 160 * 1024) per_warp /= 2;
+#define TILES(R, VPL)                                                                                                        \
+    return launch_capped_tiles<T, R, VPL>(out, ld_out, q, ld_q, k_pages, v_pages, block_table, max_blocks, positions, token_item, \
+                                          n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, s)
+    const int entries = vdim <= 64 ? 2 : (vdim <= 128 ? 4 : 8);
+    if (per_warp == 8) { if (entries == 2) TILES(8, 2); if (entries == 4) TILES(8, 4); TILES(8, 8); }
+    if (per_warp == 4) { if (entries == 2) TILES(4, 2); if (entries == 4) TILES(4, 4); TILES(4, 8); }
+    if (entries == 2) TILES(2, 2);
+    if (entries == 4) TILES(2, 4);
+    TILES(2, 8);
+#undef TILES
 }
 
 extern "C" int mllm_hybrid_capped_attention(void* out, long ld_out, const void* q, long ld_q, const void* k_pages,

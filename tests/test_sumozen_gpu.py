@@ -338,11 +338,12 @@ def test_recurrence_kernel_carries_its_state(heads, qk_heads, dim, vdim):
 
 
 @pytest.mark.parametrize("heads, kv_heads, dim, vdim, cap", [(4, 2, 16, 24, 5.0), (1, 1, 8, 8, 0.0), (6, 1, 64, 32, 2.0),
-                                                              (40, 2, 12, 70, 0.0), (3, 3, 128, 256, 9.0)])
+                                                              (40, 2, 12, 72, 0.0), (3, 3, 128, 256, 9.0), (128, 2, 64, 64, 3.0)])
 def test_attention_in_tiles_against_one_block_per_row(heads, kv_heads, dim, vdim, cap):
     """Prompt portions of three requests in one batch (one of them three tokens, so that tiles hold
     tokens of several requests), pages scattered over the pool: the tiled kernel must give what the
-    kernel with one block per (token, head) gives, and that one what the formula gives."""
+    kernel with one block per (token, head) gives, and that one what the formula gives.  (With 128
+    heads the step has enough rows for the tiles of eight rows a warp, with 40 for four.)"""
     from mini_llm_b200.kernels import ops
     torch.manual_seed(heads * 1000 + dim)
     page_size = 8
