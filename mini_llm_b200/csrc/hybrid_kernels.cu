@@ -181,7 +181,7 @@ capped_attention_plain_kernel(T* __restrict__ out, long ld_out, const T* __restr
 // ---------------------------------------------------------------------------
 // The same attention in tiles, for steps with prompt portions.  A block takes consecutive tokens
 // of the step and up to HC query heads of one key/value head: 8 * R (token, head) rows, R a warp
-// (R = 2, 4 or 8: the more rows a step has, the more of them share a block's keys).  Tokens of
+// (R = 2 or 4: a step with many rows lets more of them share a block's keys).  Tokens of
 // one request that lie side by side share every block of 32 cached keys and values, which the
 // block brings into shared memory once, in 32-bit, as 16-byte vectors asked for a block ahead.
 // Within a warp the lanes take the 32 keys of a block for the scores (a key's entries are read
@@ -205,8 +205,8 @@ template <> __device__ __forceinline__ void widen<bf16>(const uint4& v, float* d
                                                       __uint_as_float(v.w << 16), __uint_as_float(v.w & 0xffff0000u));
 }
 
-template <typename T, int R, int VPL>       // rows a warp; value entries a lane (vdim <= 32 * VPL)
-__global__ void __launch_bounds__(TILE_WARPS * 32)
+template <typename T, int R, int SIZE>      // rows a warp; the least of 64, 128, 256 that holds the key and the value size
+__global__ void __launch_bounds__(TILE_WARPS * 32, R <= 4 && SIZE <= 128 ? 2 : 1)
 capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restrict__ q, long ld_q,
                               const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                               const int* __restrict__ block_table, int max_blocks, const int* __restrict__ positions,
@@ -216,6 +216,7 @@ capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restr
     dependents_may_start();
     wait_for_earlier_kernels();
     constexpr int ROWS = TILE_WARPS * R;
+    constexpr int VPL = SIZE / 32;                           // value entries a lane
     extern __shared__ float shared[];
     const int kd = dim + 4;                                  // padded key row: lanes read rows, four entries at a time
     float* q_rows = shared;                                  // [ROWS][dim]
@@ -255,7 +256,7 @@ capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restr
     // A block of 32 keys and values comes in 16-byte vectors, up to MAXV of each per thread; which
     // (key, column) a thread's vectors are is fixed for the kernel, so no division is left in the loop.
     constexpr int VEC = 16 / (int)sizeof(T);
-    constexpr int MAXV = TILE_KEYS * CAP_MAX_HEAD / VEC / (TILE_WARPS * 32);
+    constexpr int MAXV = TILE_KEYS * SIZE / VEC / (TILE_WARPS * 32);
     uint4 key_vec[MAXV], value_vec[MAXV];
     int key_row[MAXV], key_col[MAXV], value_row[MAXV], value_col[MAXV];
 #pragma unroll
@@ -323,6 +324,7 @@ capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restr
 #pragma unroll
             for (int s = 0; s < R; s++) dot[s] = 0.0f;
             const float* kr = keys + lane * kd;
+#pragma unroll 2
             for (int d = 0; d < dim; d += 4) {
                 const float4 b = *reinterpret_cast<const float4*>(kr + d);
 #pragma unroll
@@ -353,6 +355,7 @@ capped_attention_tiled_kernel(T* __restrict__ out, long ld_out, const T* __restr
                 my_weights[lane * R + s] = e;
             }
             __syncwarp();
+#pragma unroll 4
             for (int j = 0; j < n_keys; j++) {
                 float w[R];
 #pragma unroll
@@ -400,7 +403,7 @@ extern "C" int mllm_hybrid_capped_attention_tiled_takes(int dim, int vdim, int v
            vdim <= CAP_MAX_HEAD && capped_tiled_shared(dim, vdim, 2) <= 160 * 1024;
 }
 
-template <typename T, int R, int VPL>
+template <typename T, int R, int SIZE>
 static int launch_capped_tiles(void* out, long ld_out, const void* q, long ld_q, const void* k_pages, const void* v_pages,
                                const int* block_table, int max_blocks, const int* positions, const int* token_item, int n_tokens,
                                int n_heads, int n_kv_heads, int dim, int vdim, int page_size, float scale, float cap, int window,
@@ -411,10 +414,12 @@ static int launch_capped_tiles(void* out, long ld_out, const void* q, long ld_q,
     const int tokens_per_block = ROWS / heads_per_block;
     const int chunks = (group + heads_per_block - 1) / heads_per_block;
     const size_t shared = capped_tiled_shared(dim, vdim, R);
-    cudaError_t e = cudaFuncSetAttribute(capped_attention_tiled_kernel<T, R, VPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    cudaError_t e = cudaFuncSetAttribute(capped_attention_tiled_kernel<T, R, SIZE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     if (e != cudaSuccess) return fail("capped_attention: the tiles' shared memory was refused");
+    // several blocks an SM: as much of the SM's memory as shared memory as they need
+    cudaFuncSetAttribute(capped_attention_tiled_kernel<T, R, SIZE>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     dim3 grid((n_tokens + tokens_per_block - 1) / tokens_per_block, n_kv_heads * chunks);
-    launch_kernel(g_dependent_launch != 0, capped_attention_tiled_kernel<T, R, VPL>, grid, dim3(TILE_WARPS * 32), shared, s, (T*)out,
+    launch_kernel(g_dependent_launch != 0, capped_attention_tiled_kernel<T, R, SIZE>, grid, dim3(TILE_WARPS * 32), shared, s, (T*)out,
                   ld_out, (const T*)q, ld_q, (const T*)k_pages, (const T*)v_pages, block_table, max_blocks, positions, token_item,
                   n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, tokens_per_block, heads_per_block);
     return check_launch("capped_attention_tiled_kernel");
@@ -431,20 +436,19 @@ static int launch_capped_attention(bool tiled, void* out, long ld_out, const voi
                       token_item, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window);
         return check_launch("capped_attention_plain_kernel");
     }
-    // rows a warp: the more (token, head) rows a step has, the more of them share a block's keys,
-    // as long as the blocks still fill the GPU and their shared memory fits
+    // rows a warp: four where the step has rows enough for the blocks to fill the GPU all the same
+    // (and their shared memory fits), else two
     const long rows = (long)n_tokens * n_heads;
-    int per_warp = rows >= 16384 ? 8 : (rows >= 8192 ? 4 : 2);
-    while (per_warp > 2 && capped_tiled_shared(dim, vdim, per_warp) > 160 * 1024) per_warp /= 2;
-#define TILES(R, VPL)                                                                                                        \
-    return launch_capped_tiles<T, R, VPL>(out, ld_out, q, ld_q, k_pages, v_pages, block_table, max_blocks, positions, token_item, \
-                                          n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, s)
-    const int entries = vdim <= 64 ? 2 : (vdim <= 128 ? 4 : 8);
-    if (per_warp == 8) { if (entries == 2) TILES(8, 2); if (entries == 4) TILES(8, 4); TILES(8, 8); }
-    if (per_warp == 4) { if (entries == 2) TILES(4, 2); if (entries == 4) TILES(4, 4); TILES(4, 8); }
-    if (entries == 2) TILES(2, 2);
-    if (entries == 4) TILES(2, 4);
-    TILES(2, 8);
+    int per_warp = rows >= 8192 ? 4 : 2;
+    if (capped_tiled_shared(dim, vdim, per_warp) > 160 * 1024) per_warp = 2;
+#define TILES(R, SIZE)                                                                                                        \
+    return launch_capped_tiles<T, R, SIZE>(out, ld_out, q, ld_q, k_pages, v_pages, block_table, max_blocks, positions, token_item, \
+                                           n_tokens, n_heads, n_kv_heads, dim, vdim, page_size, scale, cap, window, s)
+    const int size = (dim > vdim ? dim : vdim) <= 64 ? 64 : ((dim > vdim ? dim : vdim) <= 128 ? 128 : 256);
+    if (per_warp == 4) { if (size == 64) TILES(4, 64); if (size == 128) TILES(4, 128); TILES(4, 256); }
+    if (size == 64) TILES(2, 64);
+    if (size == 128) TILES(2, 128);
+    TILES(2, 256);
 #undef TILES
 }
 
@@ -498,14 +502,16 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
     dependents_may_start();
     wait_for_earlier_kernels();
     constexpr int COLS = 128 / LANES;
+    constexpr int PAD = DPT + 4;                           // a lane's DPT entries of a staged row, 16 bytes apart from the
+    constexpr int ROW = LANES * PAD;                       // next lane's in the banks: four entries are read at a time
     constexpr int TPR = 128 / (2 * TOK);                   // threads that bring one staged row (k or q of a token)
     constexpr int PER = (DPT * LANES + TPR - 1) / TPR;     // entries of that row a thread brings
     constexpr int VPER = (TOK * COLS + 127) / 128;         // values a thread brings
     extern __shared__ float shared[];
     const int dim = pp.dim, vdim = pp.vdim;
-    float* ks = shared;                         // [TOK][dim]
-    float* qs = ks + TOK * dim;                 // [TOK][dim]
-    float* vs = qs + TOK * dim;                 // [TOK][COLS]
+    float* ks = shared;                         // [TOK][ROW]: entry i of a row at (i / DPT) * PAD + i % DPT, zero past dim
+    float* qs = ks + TOK * ROW;                 // [TOK][ROW]
+    float* vs = qs + TOK * ROW;                 // [TOK][COLS]
     float* as = vs + TOK * COLS;                // [TOK] the step's gate, then the decay
     float* bs = as + TOK;                       // [TOK] the write gate, then the write strength
     float* kq = bs + TOK;                       // [TOK] k . q
@@ -517,11 +523,12 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
     const int lane_in = threadIdx.x % LANES, col_local = threadIdx.x / LANES;
     const int col = blockIdx.z * COLS + col_local;
     const bool live = col < vdim;
+    // this thread's part of its column of the state: rows lane_in * DPT .. + DPT - 1 (zero past dim, and it stays zero)
     float* S = pp.state + (long)pp.item_slot[item] * pp.state_stride + (long)head * dim * vdim;
     float s[DPT];
 #pragma unroll
     for (int r = 0; r < DPT; r++) {
-        const int i = lane_in + LANES * r;
+        const int i = lane_in * DPT + r;
         s[r] = (live && i < dim) ? S[(long)i * vdim + col] : 0.0f;
     }
     const float rate = expf(pp.log_rate[head]);
@@ -539,7 +546,7 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
     const int row_token = row >> 1;
     const T* row_base = (row & 1) ? q : k;
     const long row_ld = (row & 1) ? pp.ld_q : pp.ld_k;
-    float* row_smem = ((row & 1) ? qs : ks) + row_token * dim;
+    float* row_smem = ((row & 1) ? qs : ks) + row_token * ROW;
     T raw[PER], raw_v[VPER];
     float raw_a = 0.0f, raw_b = 0.0f;
     auto ask = [&](int start) {
@@ -567,7 +574,7 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
 #pragma unroll
         for (int i = 0; i < PER; i++) {
             const int d = row_sub + TPR * i;
-            if (d < dim) row_smem[d] = to_f32(raw[i]);
+            if (d < DPT * LANES) row_smem[(d / DPT) * PAD + d % DPT] = to_f32(raw[i]);       // (zero past dim)
         }
 #pragma unroll
         for (int i = 0; i < VPER; i++) {
@@ -578,20 +585,23 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
         __syncthreads();
         // a warp finishes a token: unit vectors if asked, k . q, the step, the decay, the write strength
         for (int tt = warp; tt < n; tt += 4) {
+            float* kt = ks + tt * ROW;
+            float* qt = qs + tt * ROW;
             float fk = 1.0f, fq = pp.q_scale;
             if (pp.unit_norm) {
                 float sk = 0.0f, sq = 0.0f;
-                for (int d = lane; d < dim; d += 32) {
-                    const float kv = ks[tt * dim + d], qv = qs[tt * dim + d];
+                for (int d = lane; d < DPT * LANES; d += 32) {
+                    const float kv = kt[(d / DPT) * PAD + d % DPT], qv = qt[(d / DPT) * PAD + d % DPT];
                     sk = fmaf(kv, kv, sk), sq = fmaf(qv, qv, sq);
                 }
                 fk = 1.0f / sqrtf(warp_sum(sk) + 1e-6f);
                 fq = pp.q_scale / sqrtf(warp_sum(sq) + 1e-6f);
             }
             float dot = 0.0f;
-            for (int d = lane; d < dim; d += 32) {
-                const float kv = ks[tt * dim + d] * fk, qv = qs[tt * dim + d] * fq;
-                ks[tt * dim + d] = kv, qs[tt * dim + d] = qv;
+            for (int d = lane; d < DPT * LANES; d += 32) {
+                const int at = (d / DPT) * PAD + d % DPT;
+                const float kv = kt[at] * fk, qv = qt[at] * fq;
+                kt[at] = kv, qt[at] = qv;
                 dot = fmaf(kv, qv, dot);
             }
             dot = warp_sum(dot);
@@ -606,13 +616,19 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
         __syncthreads();
         if (start + TOK < count) ask(start + TOK);
         for (int tt = 0; tt < n; tt++) {
-            const float* kr = ks + tt * dim;
-            const float* qr = qs + tt * dim;
+            const float* kr = ks + tt * ROW + lane_in * PAD;
+            const float* qr = qs + tt * ROW + lane_in * PAD;
+            float kreg[DPT];
             float dk[2] = {0.0f, 0.0f}, dq[2] = {0.0f, 0.0f};      // two chains each: half the latency
 #pragma unroll
-            for (int r = 0; r < DPT; r++) {
-                const int i = lane_in + LANES * r;
-                if (i < dim) dk[r & 1] = fmaf(s[r], kr[i], dk[r & 1]), dq[r & 1] = fmaf(s[r], qr[i], dq[r & 1]);
+            for (int r = 0; r < DPT; r += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(kr + r);
+                const float4 q4 = *reinterpret_cast<const float4*>(qr + r);
+                kreg[r] = k4.x, kreg[r + 1] = k4.y, kreg[r + 2] = k4.z, kreg[r + 3] = k4.w;
+                dk[0] = fmaf(s[r], k4.x, dk[0]), dq[0] = fmaf(s[r], q4.x, dq[0]);
+                dk[1] = fmaf(s[r + 1], k4.y, dk[1]), dq[1] = fmaf(s[r + 1], q4.y, dq[1]);
+                dk[0] = fmaf(s[r + 2], k4.z, dk[0]), dq[0] = fmaf(s[r + 2], q4.z, dq[0]);
+                dk[1] = fmaf(s[r + 3], k4.w, dk[1]), dq[1] = fmaf(s[r + 3], q4.w, dq[1]);
             }
             float sum_k = dk[0] + dk[1], sum_q = dq[0] + dq[1];
 #pragma unroll
@@ -623,10 +639,7 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
             const float a = as[tt], b = bs[tt], value = vs[tt * COLS + col_local];
             const float u = pp.delta ? b * (value - a * sum_k) : b * value;
 #pragma unroll
-            for (int r = 0; r < DPT; r++) {
-                const int i = lane_in + LANES * r;
-                if (i < dim) s[r] = fmaf(kr[i], u, a * s[r]);
-            }
+            for (int r = 0; r < DPT; r++) s[r] = fmaf(kreg[r], u, a * s[r]);
             if (live && lane_in == 0)
                 pp.out[(first + start + tt) * pp.ld_out + (long)head * vdim + col] = fmaf(u, kq[tt], a * sum_q) + skip * value;
         }
@@ -634,7 +647,7 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
     if (pp.writes && live) {
 #pragma unroll
         for (int r = 0; r < DPT; r++) {
-            const int i = lane_in + LANES * r;
+            const int i = lane_in * DPT + r;
             if (i < dim) S[(long)i * vdim + col] = s[r];
         }
     }
@@ -643,20 +656,23 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
 template <typename T, int DPT, int LANES, int TOK>
 static int launch_recurrence(const RecurrenceParams& pp, int n_items, cudaStream_t s) {
     constexpr int COLS = 128 / LANES;
-    const size_t shared = sizeof(float) * ((size_t)2 * TOK * pp.dim + TOK * COLS + 3 * TOK);
+    const size_t shared = sizeof(float) * ((size_t)2 * TOK * LANES * (DPT + 4) + TOK * COLS + 3 * TOK);
     dim3 grid(n_items, pp.heads, (pp.vdim + COLS - 1) / COLS);
+    if (shared > 48 * 1024 &&
+        cudaFuncSetAttribute(linear_recurrence_kernel<T, DPT, LANES, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared) != cudaSuccess)
+        return fail("linear_recurrence: the staged rows' shared memory was refused");
     launch_kernel(g_dependent_launch != 0, linear_recurrence_kernel<T, DPT, LANES, TOK>, grid, dim3(128), shared, s, pp);
     return check_launch("linear_recurrence_kernel");
 }
 
-// A column of the state over 4 lanes for small keys, over 8 from 33 entries on (shorter sums, more
-// blocks for the same state), over a whole warp past 256.
+// A column of the state lies in the registers of 4 to 32 lanes of a warp, eight rows a lane up to
+// a key size of 256 (short sums, and more blocks for the same state), 32 rows a lane past that.
 template <typename T>
 static int pick_recurrence(const RecurrenceParams& pp, int n_items, cudaStream_t s) {
     if (pp.dim <= 32) return launch_recurrence<T, 8, 4, 16>(pp, n_items, s);
     if (pp.dim <= 64) return launch_recurrence<T, 8, 8, 16>(pp, n_items, s);
-    if (pp.dim <= 128) return launch_recurrence<T, 16, 8, 16>(pp, n_items, s);
-    if (pp.dim <= 256) return launch_recurrence<T, 32, 8, 16>(pp, n_items, s);
+    if (pp.dim <= 128) return launch_recurrence<T, 8, 16, 16>(pp, n_items, s);
+    if (pp.dim <= 256) return launch_recurrence<T, 8, 32, 16>(pp, n_items, s);
     return launch_recurrence<T, 32, 32, 4>(pp, n_items, s);
 }
 

@@ -342,8 +342,8 @@ def test_recurrence_kernel_carries_its_state(heads, qk_heads, dim, vdim):
 def test_attention_in_tiles_against_one_block_per_row(heads, kv_heads, dim, vdim, cap):
     """Prompt portions of three requests in one batch (one of them three tokens, so that tiles hold
     tokens of several requests), pages scattered over the pool: the tiled kernel must give what the
-    kernel with one block per (token, head) gives, and that one what the formula gives.  (With 128
-    heads the step has enough rows for the tiles of eight rows a warp, with 40 for four.)"""
+    kernel with one block per (token, head) gives, and that one what the formula gives.  (With 40
+    and 128 heads the step has rows enough for the tiles of four rows a warp.)"""
     from mini_llm_b200.kernels import ops
     torch.manual_seed(heads * 1000 + dim)
     page_size = 8
