@@ -525,12 +525,20 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
     const bool live = col < vdim;
     // this thread's part of its column of the state: rows lane_in * DPT .. + DPT - 1 (zero past dim, and it stays zero)
     float* S = pp.state + (long)pp.item_slot[item] * pp.state_stride + (long)head * dim * vdim;
+    // (the block's slice of the state goes through shared memory both ways, so that the global
+    // reads and writes run along the rows of S, whatever the lanes' share of a column is)
     float s[DPT];
+    for (int u = threadIdx.x; u < dim * COLS; u += 128) {
+        const int i = u / COLS, c = blockIdx.z * COLS + u % COLS;
+        shared[u] = c < vdim ? S[(long)i * vdim + c] : 0.0f;
+    }
+    __syncthreads();
 #pragma unroll
     for (int r = 0; r < DPT; r++) {
         const int i = lane_in * DPT + r;
-        s[r] = (live && i < dim) ? S[(long)i * vdim + col] : 0.0f;
+        s[r] = i < dim ? shared[i * COLS + col_local] : 0.0f;
     }
+    __syncthreads();
     const float rate = expf(pp.log_rate[head]);
     const float bias = pp.step_bias[head];
     const float skip = pp.skip != nullptr ? pp.skip[head] : 0.0f;
@@ -644,11 +652,17 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
                 pp.out[(first + start + tt) * pp.ld_out + (long)head * vdim + col] = fmaf(u, kq[tt], a * sum_q) + skip * value;
         }
     }
-    if (pp.writes && live) {
+    if (pp.writes) {
+        __syncthreads();
 #pragma unroll
         for (int r = 0; r < DPT; r++) {
             const int i = lane_in * DPT + r;
-            if (i < dim) S[(long)i * vdim + col] = s[r];
+            if (i < dim) shared[i * COLS + col_local] = s[r];
+        }
+        __syncthreads();
+        for (int u = threadIdx.x; u < dim * COLS; u += 128) {
+            const int i = u / COLS, c = blockIdx.z * COLS + u % COLS;
+            if (c < vdim) S[(long)i * vdim + c] = shared[u];
         }
     }
 }
