@@ -679,18 +679,25 @@ static int launch_recurrence(const RecurrenceParams& pp, int n_items, cudaStream
     return check_launch("linear_recurrence_kernel");
 }
 
-// A column of the state lies in the registers of 4 to 32 lanes of a warp, eight rows a lane up to
-// a key size of 256 (short sums, and more blocks for the same state), 32 rows a lane past that.
+// A column of the state lies in the registers of 4 to 32 lanes of a warp.  Prompt portions: eight
+// rows a lane up to a key size of 256 (short sums, and many blocks for the same state, each with
+// its tokens to walk).  Steps of few tokens per entry: as many rows a lane as registers hold, so
+// that the blocks, each of which pays the same chain of loads for its one token, are few.
 template <typename T>
-static int pick_recurrence(const RecurrenceParams& pp, int n_items, cudaStream_t s) {
+static int pick_recurrence(const RecurrenceParams& pp, int n_items, bool few_tokens, cudaStream_t s) {
     if (pp.dim <= 32) return launch_recurrence<T, 8, 4, 16>(pp, n_items, s);
-    if (pp.dim <= 64) return launch_recurrence<T, 8, 8, 16>(pp, n_items, s);
-    if (pp.dim <= 128) return launch_recurrence<T, 8, 16, 16>(pp, n_items, s);
+    if (few_tokens) {
+        if (pp.dim <= 64) return launch_recurrence<T, 16, 4, 16>(pp, n_items, s);
+        if (pp.dim <= 128) return launch_recurrence<T, 32, 4, 16>(pp, n_items, s);
+    } else {
+        if (pp.dim <= 64) return launch_recurrence<T, 8, 8, 16>(pp, n_items, s);
+        if (pp.dim <= 128) return launch_recurrence<T, 8, 16, 16>(pp, n_items, s);
+    }
     if (pp.dim <= 256) return launch_recurrence<T, 8, 32, 16>(pp, n_items, s);
     return launch_recurrence<T, 32, 32, 4>(pp, n_items, s);
 }
 
-extern "C" int mllm_hybrid_linear_recurrence(const RecurrenceParams* params, int n_items, int dtype, void* stream) {
+extern "C" int mllm_hybrid_linear_recurrence(const RecurrenceParams* params, int n_items, int n_tokens, int dtype, void* stream) {
     if (n_items <= 0) return 0;
     const RecurrenceParams& pp = *params;
     if (pp.dim <= 0 || pp.dim > 1024 || pp.vdim <= 0) return fail("linear_recurrence: the key size must be in 1..1024");
@@ -698,8 +705,9 @@ extern "C" int mllm_hybrid_linear_recurrence(const RecurrenceParams* params, int
     if (pp.heads > 65535) return fail("linear_recurrence: too many heads for one launch");
     if (pp.delta && pp.gate_b == nullptr) return fail("linear_recurrence: the delta rule needs its write gates");
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == DT_F32) return pick_recurrence<float>(pp, n_items, s);
-    if (dtype == DT_BF16) return pick_recurrence<bf16>(pp, n_items, s);
+    const bool few_tokens = n_tokens <= 4 * n_items;
+    if (dtype == DT_F32) return pick_recurrence<float>(pp, n_items, few_tokens, s);
+    if (dtype == DT_BF16) return pick_recurrence<bf16>(pp, n_items, few_tokens, s);
     return fail("linear_recurrence: unknown dtype");
 }
 

@@ -1219,7 +1219,7 @@ class _RecurrenceParams(ctypes.Structure):
                 ("writes", I)]
 
 
-_linear_recurrence = Function("hybrid", "mllm_hybrid_linear_recurrence", [ctypes.POINTER(_RecurrenceParams), I, I, P])
+_linear_recurrence = Function("hybrid", "mllm_hybrid_linear_recurrence", [ctypes.POINTER(_RecurrenceParams), I, I, I, P])
 
 
 def linear_recurrence(out, q, k, v, gate_a, gate_b, log_rate, step_bias, state, item_slot, item_offset, item_count, heads,
@@ -1260,7 +1260,7 @@ def linear_recurrence(out, q, k, v, gate_a, gate_b, log_rate, step_bias, state, 
     params.item_slot, params.item_offset, params.item_count = item_slot.data_ptr(), item_offset.data_ptr(), item_count.data_ptr()
     params.heads, params.qk_heads, params.dim, params.vdim = heads, qk_heads, dim, vdim
     params.q_scale, params.delta, params.unit_norm, params.writes = float(q_scale), int(bool(delta)), int(bool(unit_norm)), int(bool(writes))
-    _linear_recurrence(ctypes.byref(params), item_count.shape[0], dtype_code(q.dtype), _stream())
+    _linear_recurrence(ctypes.byref(params), item_count.shape[0], n, dtype_code(q.dtype), _stream())
     return out
 
 

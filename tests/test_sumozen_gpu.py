@@ -297,7 +297,7 @@ def test_taps_kernel_with_bias_and_activation_over_cuts():
 @pytest.mark.parametrize("heads, qk_heads, dim, vdim", [(2, 1, 12, 37), (3, 3, 40, 8), (4, 2, 70, 33), (1, 1, 130, 20),
                                                         (2, 2, 300, 6)])
 def test_recurrence_kernel_carries_its_state(heads, qk_heads, dim, vdim):
-    """Both forms, a sequence cut in five (down to one token), against the token-by-token formulas."""
+    """Both forms, a sequence cut in six (down to one token), against the token-by-token formulas."""
     from mini_llm_b200.kernels import ops
     rng = np.random.default_rng(dim)
     n = 100
@@ -326,12 +326,15 @@ def test_recurrence_kernel_carries_its_state(heads, qk_heads, dim, vdim):
                     expected[t, head] = S.T @ qt + skip[head] * vt
         state = torch.zeros((2, heads * dim * vdim), dtype=torch.float32, device="cuda")
         out = torch.empty((n, heads * vdim), dtype=torch.float32, device="cuda")
-        for first, count in ((0, 1), (1, 9), (10, 13), (23, 32), (55, 45)):
-            # entry 0 is another request with no tokens in this step; entry 1 is ours, in slot 1
-            ops.linear_recurrence(out, dev(q), dev(k), dev(v), dev(gate_a), dev(gate_b) if delta else None, dev(log_rate),
-                                  dev(bias), state, dev([0, 1], torch.int32), dev([0, first], torch.int32),
-                                  dev([0, count], torch.int32), heads, qk_heads, dim, vdim, delta, unit_norm=delta,
-                                  q_scale=0.5 if delta else 1.0, skip=None if delta else dev(skip))
+        for first, count in ((0, 1), (1, 9), (10, 3), (13, 10), (23, 32), (55, 45)):
+            # entry 0 is another request with no tokens in this step; entry 1 is ours, in slot 1.  The step
+            # holds the portion's rows only: short portions take the kernel's form for few tokens an entry.
+            rows = slice(first, first + count)
+            ops.linear_recurrence(out[rows], dev(q[rows]), dev(k[rows]), dev(v[rows]), dev(gate_a[rows]),
+                                  dev(gate_b[rows]) if delta else None, dev(log_rate), dev(bias), state,
+                                  dev([0, 1], torch.int32), dev([0, 0], torch.int32), dev([0, count], torch.int32), heads,
+                                  qk_heads, dim, vdim, delta, unit_norm=delta, q_scale=0.5 if delta else 1.0,
+                                  skip=None if delta else dev(skip))
         np.testing.assert_allclose(out.cpu().numpy(), expected.reshape(n, heads * vdim), rtol=5e-5, atol=2e-5,
                                    err_msg=f"delta {delta}")
         assert float(state[0].abs().max()) == 0.0
