@@ -497,11 +497,12 @@ struct RecurrenceParams {
     int delta, unit_norm, writes;
 };
 
-template <typename T, int DPT, int LANES, int TOK>
+template <typename T, int DPT, int LANES, int TOK, int CPT>      // CPT: columns of the state a thread takes
 __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams pp) {
     dependents_may_start();
     wait_for_earlier_kernels();
-    constexpr int COLS = 128 / LANES;
+    constexpr int GROUPS = 128 / LANES;                    // groups of lanes; each takes CPT columns of the state,
+    constexpr int COLS = GROUPS * CPT;                     // GROUPS apart, whose chains of sums run side by side
     constexpr int PAD = DPT + 4;                           // a lane's DPT entries of a staged row, 16 bytes apart from the
     constexpr int ROW = LANES * PAD;                       // next lane's in the banks: four entries are read at a time
     constexpr int TPR = 128 / (2 * TOK);                   // threads that bring one staged row (k or q of a token)
@@ -521,13 +522,12 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
     const long first = pp.item_offset[item];
     const int qk_head = head / (pp.heads / pp.qk_heads);
     const int lane_in = threadIdx.x % LANES, col_local = threadIdx.x / LANES;
-    const int col = blockIdx.z * COLS + col_local;
-    const bool live = col < vdim;
+    // this thread's columns: col_local, col_local + GROUPS, ... of the block's COLS
     // this thread's part of its column of the state: rows lane_in * DPT .. + DPT - 1 (zero past dim, and it stays zero)
     float* S = pp.state + (long)pp.item_slot[item] * pp.state_stride + (long)head * dim * vdim;
     // (the block's slice of the state goes through shared memory both ways, so that the global
     // reads and writes run along the rows of S, whatever the lanes' share of a column is)
-    float s[DPT];
+    float s[CPT][DPT];
     for (int u = threadIdx.x; u < dim * COLS; u += 128) {
         const int i = u / COLS, c = blockIdx.z * COLS + u % COLS;
         shared[u] = c < vdim ? S[(long)i * vdim + c] : 0.0f;
@@ -536,7 +536,8 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
 #pragma unroll
     for (int r = 0; r < DPT; r++) {
         const int i = lane_in * DPT + r;
-        s[r] = i < dim ? shared[i * COLS + col_local] : 0.0f;
+#pragma unroll
+        for (int c = 0; c < CPT; c++) s[c][r] = i < dim ? shared[i * COLS + col_local + c * GROUPS] : 0.0f;
     }
     __syncthreads();
     const float rate = expf(pp.log_rate[head]);
@@ -589,36 +590,49 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
             const int u = threadIdx.x + 128 * i;
             if (u < TOK * COLS) vs[u] = to_f32(raw_v[i]);
         }
-        if (threadIdx.x < TOK) as[threadIdx.x] = raw_a, bs[threadIdx.x] = raw_b;
+        if (threadIdx.x < TOK) {
+            // a thread a token: the step, the decay, the write strength
+            const float step = softplus_f(raw_a + bias);
+            as[threadIdx.x] = expf(-rate * step);
+            bs[threadIdx.x] = pp.delta ? sigmoid_f(raw_b) : step;
+        }
         __syncthreads();
-        // a warp finishes a token: unit vectors if asked, k . q, the step, the decay, the write strength
-        for (int tt = warp; tt < n; tt += 4) {
-            float* kt = ks + tt * ROW;
-            float* qt = qs + tt * ROW;
-            float fk = 1.0f, fq = pp.q_scale;
-            if (pp.unit_norm) {
-                float sk = 0.0f, sq = 0.0f;
-                for (int d = lane; d < DPT * LANES; d += 32) {
-                    const float kv = kt[(d / DPT) * PAD + d % DPT], qv = qt[(d / DPT) * PAD + d % DPT];
-                    sk = fmaf(kv, kv, sk), sq = fmaf(qv, qv, sq);
+        // a warp finishes TOK / 4 tokens: unit vectors if asked, and k . q; the sums of its tokens are
+        // taken side by side, so that their exchanges between the lanes lie under one another
+        {
+            constexpr int MINE = TOK / 4;
+            float sk[MINE], sq[MINE], sd[MINE];
+#pragma unroll
+            for (int j = 0; j < MINE; j++) {
+                const int tt = warp + 4 * j;
+                sk[j] = sq[j] = sd[j] = 0.0f;
+                if (tt < n)
+                    for (int d = lane; d < DPT * LANES; d += 32) {
+                        const int at = tt * ROW + (d / DPT) * PAD + d % DPT;
+                        const float kv = ks[at], qv = qs[at];
+                        sk[j] = fmaf(kv, kv, sk[j]), sq[j] = fmaf(qv, qv, sq[j]), sd[j] = fmaf(kv, qv, sd[j]);
+                    }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                for (int j = 0; j < MINE; j++) {
+                    sk[j] += __shfl_xor_sync(0xffffffffu, sk[j], o);
+                    sq[j] += __shfl_xor_sync(0xffffffffu, sq[j], o);
+                    sd[j] += __shfl_xor_sync(0xffffffffu, sd[j], o);
                 }
-                fk = 1.0f / sqrtf(warp_sum(sk) + 1e-6f);
-                fq = pp.q_scale / sqrtf(warp_sum(sq) + 1e-6f);
-            }
-            float dot = 0.0f;
-            for (int d = lane; d < DPT * LANES; d += 32) {
-                const int at = (d / DPT) * PAD + d % DPT;
-                const float kv = kt[at] * fk, qv = qt[at] * fq;
-                kt[at] = kv, qt[at] = qv;
-                dot = fmaf(kv, qv, dot);
-            }
-            dot = warp_sum(dot);
-            if (lane == 0) {
-                const float step = softplus_f(as[tt] + bias);
-                const float write = pp.delta ? sigmoid_f(bs[tt]) : step;
-                as[tt] = expf(-rate * step);
-                bs[tt] = write;
-                kq[tt] = dot;
+#pragma unroll
+            for (int j = 0; j < MINE; j++) {
+                const int tt = warp + 4 * j;
+                if (tt >= n) continue;
+                const float fk = pp.unit_norm ? 1.0f / sqrtf(sk[j] + 1e-6f) : 1.0f;
+                const float fq = pp.unit_norm ? pp.q_scale / sqrtf(sq[j] + 1e-6f) : pp.q_scale;
+                if (pp.unit_norm || fq != 1.0f)
+                    for (int d = lane; d < DPT * LANES; d += 32) {
+                        const int at = tt * ROW + (d / DPT) * PAD + d % DPT;
+                        ks[at] *= fk, qs[at] *= fq;
+                    }
+                if (lane == 0) kq[tt] = sd[j] * fk * fq;
             }
         }
         __syncthreads();
@@ -627,29 +641,43 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
             const float* kr = ks + tt * ROW + lane_in * PAD;
             const float* qr = qs + tt * ROW + lane_in * PAD;
             float kreg[DPT];
-            float dk[2] = {0.0f, 0.0f}, dq[2] = {0.0f, 0.0f};      // two chains each: half the latency
+            float dk[CPT][2], dq[CPT][2];                      // two chains each: half the latency
+#pragma unroll
+            for (int c = 0; c < CPT; c++) dk[c][0] = dk[c][1] = dq[c][0] = dq[c][1] = 0.0f;
 #pragma unroll
             for (int r = 0; r < DPT; r += 4) {
                 const float4 k4 = *reinterpret_cast<const float4*>(kr + r);
                 const float4 q4 = *reinterpret_cast<const float4*>(qr + r);
                 kreg[r] = k4.x, kreg[r + 1] = k4.y, kreg[r + 2] = k4.z, kreg[r + 3] = k4.w;
-                dk[0] = fmaf(s[r], k4.x, dk[0]), dq[0] = fmaf(s[r], q4.x, dq[0]);
-                dk[1] = fmaf(s[r + 1], k4.y, dk[1]), dq[1] = fmaf(s[r + 1], q4.y, dq[1]);
-                dk[0] = fmaf(s[r + 2], k4.z, dk[0]), dq[0] = fmaf(s[r + 2], q4.z, dq[0]);
-                dk[1] = fmaf(s[r + 3], k4.w, dk[1]), dq[1] = fmaf(s[r + 3], q4.w, dq[1]);
-            }
-            float sum_k = dk[0] + dk[1], sum_q = dq[0] + dq[1];
 #pragma unroll
-            for (int o = LANES / 2; o > 0; o >>= 1) {
-                sum_k += __shfl_xor_sync(0xffffffffu, sum_k, o);
-                sum_q += __shfl_xor_sync(0xffffffffu, sum_q, o);
+                for (int c = 0; c < CPT; c++) {
+                    dk[c][0] = fmaf(s[c][r], k4.x, dk[c][0]), dq[c][0] = fmaf(s[c][r], q4.x, dq[c][0]);
+                    dk[c][1] = fmaf(s[c][r + 1], k4.y, dk[c][1]), dq[c][1] = fmaf(s[c][r + 1], q4.y, dq[c][1]);
+                    dk[c][0] = fmaf(s[c][r + 2], k4.z, dk[c][0]), dq[c][0] = fmaf(s[c][r + 2], q4.z, dq[c][0]);
+                    dk[c][1] = fmaf(s[c][r + 3], k4.w, dk[c][1]), dq[c][1] = fmaf(s[c][r + 3], q4.w, dq[c][1]);
+                }
             }
-            const float a = as[tt], b = bs[tt], value = vs[tt * COLS + col_local];
-            const float u = pp.delta ? b * (value - a * sum_k) : b * value;
+            float sum_k[CPT], sum_q[CPT];
 #pragma unroll
-            for (int r = 0; r < DPT; r++) s[r] = fmaf(kreg[r], u, a * s[r]);
-            if (live && lane_in == 0)
-                pp.out[(first + start + tt) * pp.ld_out + (long)head * vdim + col] = fmaf(u, kq[tt], a * sum_q) + skip * value;
+            for (int c = 0; c < CPT; c++) sum_k[c] = dk[c][0] + dk[c][1], sum_q[c] = dq[c][0] + dq[c][1];
+#pragma unroll
+            for (int o = LANES / 2; o > 0; o >>= 1)
+#pragma unroll
+                for (int c = 0; c < CPT; c++) {
+                    sum_k[c] += __shfl_xor_sync(0xffffffffu, sum_k[c], o);
+                    sum_q[c] += __shfl_xor_sync(0xffffffffu, sum_q[c], o);
+                }
+            const float a = as[tt], b = bs[tt], both = kq[tt];
+#pragma unroll
+            for (int c = 0; c < CPT; c++) {
+                const float value = vs[tt * COLS + col_local + c * GROUPS];
+                const float u = pp.delta ? b * (value - a * sum_k[c]) : b * value;
+#pragma unroll
+                for (int r = 0; r < DPT; r++) s[c][r] = fmaf(kreg[r], u, a * s[c][r]);
+                const int col = blockIdx.z * COLS + col_local + c * GROUPS;
+                if (col < vdim && lane_in == 0)
+                    pp.out[(first + start + tt) * pp.ld_out + (long)head * vdim + col] = fmaf(u, both, a * sum_q[c]) + skip * value;
+            }
         }
     }
     if (pp.writes) {
@@ -657,7 +685,9 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
 #pragma unroll
         for (int r = 0; r < DPT; r++) {
             const int i = lane_in * DPT + r;
-            if (i < dim) shared[i * COLS + col_local] = s[r];
+#pragma unroll
+            for (int c = 0; c < CPT; c++)
+                if (i < dim) shared[i * COLS + col_local + c * GROUPS] = s[c][r];
         }
         __syncthreads();
         for (int u = threadIdx.x; u < dim * COLS; u += 128) {
@@ -667,15 +697,15 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
     }
 }
 
-template <typename T, int DPT, int LANES, int TOK>
+template <typename T, int DPT, int LANES, int TOK, int CPT>
 static int launch_recurrence(const RecurrenceParams& pp, int n_items, cudaStream_t s) {
-    constexpr int COLS = 128 / LANES;
+    constexpr int COLS = 128 / LANES * CPT;
     const size_t shared = sizeof(float) * ((size_t)2 * TOK * LANES * (DPT + 4) + TOK * COLS + 3 * TOK);
     dim3 grid(n_items, pp.heads, (pp.vdim + COLS - 1) / COLS);
     if (shared > 48 * 1024 &&
-        cudaFuncSetAttribute(linear_recurrence_kernel<T, DPT, LANES, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared) != cudaSuccess)
+        cudaFuncSetAttribute(linear_recurrence_kernel<T, DPT, LANES, TOK, CPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared) != cudaSuccess)
         return fail("linear_recurrence: the staged rows' shared memory was refused");
-    launch_kernel(g_dependent_launch != 0, linear_recurrence_kernel<T, DPT, LANES, TOK>, grid, dim3(128), shared, s, pp);
+    launch_kernel(g_dependent_launch != 0, linear_recurrence_kernel<T, DPT, LANES, TOK, CPT>, grid, dim3(128), shared, s, pp);
     return check_launch("linear_recurrence_kernel");
 }
 
@@ -685,16 +715,18 @@ static int launch_recurrence(const RecurrenceParams& pp, int n_items, cudaStream
 // that the blocks, each of which pays the same chain of loads for its one token, are few.
 template <typename T>
 static int pick_recurrence(const RecurrenceParams& pp, int n_items, bool few_tokens, cudaStream_t s) {
-    if (pp.dim <= 32) return launch_recurrence<T, 8, 4, 16>(pp, n_items, s);
+    if (pp.dim <= 32) return launch_recurrence<T, 8, 4, 16, 1>(pp, n_items, s);
     if (few_tokens) {
-        if (pp.dim <= 64) return launch_recurrence<T, 16, 4, 16>(pp, n_items, s);
-        if (pp.dim <= 128) return launch_recurrence<T, 32, 4, 16>(pp, n_items, s);
+        if (pp.dim <= 64) return launch_recurrence<T, 16, 4, 16, 1>(pp, n_items, s);
+        if (pp.dim <= 128) return launch_recurrence<T, 32, 4, 16, 1>(pp, n_items, s);
     } else {
-        if (pp.dim <= 64) return launch_recurrence<T, 8, 8, 16>(pp, n_items, s);
-        if (pp.dim <= 128) return launch_recurrence<T, 8, 16, 16>(pp, n_items, s);
+        // (two columns a thread: the walk from token to token is a chain of dependent sums and
+        // exchanges between lanes, and a second column's chain runs in the gaps of the first)
+        if (pp.dim <= 64) return launch_recurrence<T, 8, 8, 16, 2>(pp, n_items, s);
+        if (pp.dim <= 128) return launch_recurrence<T, 8, 16, 16, 2>(pp, n_items, s);
     }
-    if (pp.dim <= 256) return launch_recurrence<T, 8, 32, 16>(pp, n_items, s);
-    return launch_recurrence<T, 32, 32, 4>(pp, n_items, s);
+    if (pp.dim <= 256) return launch_recurrence<T, 8, 32, 16, 2>(pp, n_items, s);
+    return launch_recurrence<T, 32, 32, 4, 1>(pp, n_items, s);
 }
 
 extern "C" int mllm_hybrid_linear_recurrence(const RecurrenceParams* params, int n_items, int n_tokens, int dtype, void* stream) {
