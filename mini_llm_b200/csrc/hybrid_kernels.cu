@@ -700,7 +700,9 @@ __global__ void __launch_bounds__(128) linear_recurrence_kernel(RecurrenceParams
 template <typename T, int DPT, int LANES, int TOK, int CPT>
 static int launch_recurrence(const RecurrenceParams& pp, int n_items, cudaStream_t s) {
     constexpr int COLS = 128 / LANES * CPT;
-    const size_t shared = sizeof(float) * ((size_t)2 * TOK * LANES * (DPT + 4) + TOK * COLS + 3 * TOK);
+    // the staged chunk, or the block's slice of the state on its way in and out, whichever is larger
+    const size_t staged = (size_t)2 * TOK * LANES * (DPT + 4) + TOK * COLS + 3 * TOK, slice = (size_t)DPT * LANES * COLS;
+    const size_t shared = sizeof(float) * (staged > slice ? staged : slice);
     dim3 grid(n_items, pp.heads, (pp.vdim + COLS - 1) / COLS);
     if (shared > 48 * 1024 &&
         cudaFuncSetAttribute(linear_recurrence_kernel<T, DPT, LANES, TOK, CPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared) != cudaSuccess)
@@ -710,20 +712,33 @@ static int launch_recurrence(const RecurrenceParams& pp, int n_items, cudaStream
 }
 
 // A column of the state lies in the registers of 4 to 32 lanes of a warp.  Prompt portions: eight
-// rows a lane up to a key size of 256 (short sums, and many blocks for the same state, each with
-// its tokens to walk).  Steps of few tokens per entry: as many rows a lane as registers hold, so
-// that the blocks, each of which pays the same chain of loads for its one token, are few.
+// rows a lane up to a key size of 256 (short sums).  Steps of few tokens per entry: as many rows a
+// lane as registers hold, so that the blocks, each of which pays the same chain of loads for its
+// one token, are few.
 template <typename T>
-static int pick_recurrence(const RecurrenceParams& pp, int n_items, bool few_tokens, cudaStream_t s) {
+static int pick_recurrence(const RecurrenceParams& pp, int n_items, int n_tokens, cudaStream_t s) {
     if (pp.dim <= 32) return launch_recurrence<T, 8, 4, 16, 1>(pp, n_items, s);
-    if (few_tokens) {
+    if (n_tokens <= 4 * n_items) {
         if (pp.dim <= 64) return launch_recurrence<T, 16, 4, 16, 1>(pp, n_items, s);
         if (pp.dim <= 128) return launch_recurrence<T, 32, 4, 16, 1>(pp, n_items, s);
-    } else {
-        // (two columns a thread: the walk from token to token is a chain of dependent sums and
-        // exchanges between lanes, and a second column's chain runs in the gaps of the first)
-        if (pp.dim <= 64) return launch_recurrence<T, 8, 8, 16, 2>(pp, n_items, s);
-        if (pp.dim <= 128) return launch_recurrence<T, 8, 16, 16, 2>(pp, n_items, s);
+    } else if (pp.dim <= 128) {
+        // Prompt portions.  The walk from token to token is a chain of dependent sums and exchanges
+        // between lanes, about as long whatever a thread holds; so a thread takes 2, 4 or 8 columns,
+        // whose chains run in one another's gaps: the fewest that leave the busy entries' blocks
+        // (entries of a step that is filled up to a round shape may be empty) one an SM.
+        const int groups = pp.dim <= 64 ? 16 : 8;
+        int busy = (n_tokens + 255) / 256;
+        if (busy > n_items) busy = n_items;
+        int columns = 2;
+        while (columns < 8 && (long)busy * pp.heads * ((pp.vdim + groups * columns - 1) / (groups * columns)) > 148) columns *= 2;
+        if (pp.dim <= 64) {
+            if (columns == 2) return launch_recurrence<T, 8, 8, 16, 2>(pp, n_items, s);
+            if (columns == 4) return launch_recurrence<T, 8, 8, 16, 4>(pp, n_items, s);
+            return launch_recurrence<T, 8, 8, 16, 8>(pp, n_items, s);
+        }
+        if (columns == 2) return launch_recurrence<T, 8, 16, 16, 2>(pp, n_items, s);
+        if (columns == 4) return launch_recurrence<T, 8, 16, 16, 4>(pp, n_items, s);
+        return launch_recurrence<T, 8, 16, 16, 8>(pp, n_items, s);
     }
     if (pp.dim <= 256) return launch_recurrence<T, 8, 32, 16, 2>(pp, n_items, s);
     return launch_recurrence<T, 32, 32, 4, 1>(pp, n_items, s);
@@ -737,9 +752,8 @@ extern "C" int mllm_hybrid_linear_recurrence(const RecurrenceParams* params, int
     if (pp.heads > 65535) return fail("linear_recurrence: too many heads for one launch");
     if (pp.delta && pp.gate_b == nullptr) return fail("linear_recurrence: the delta rule needs its write gates");
     cudaStream_t s = (cudaStream_t)stream;
-    const bool few_tokens = n_tokens <= 4 * n_items;
-    if (dtype == DT_F32) return pick_recurrence<float>(pp, n_items, few_tokens, s);
-    if (dtype == DT_BF16) return pick_recurrence<bf16>(pp, n_items, few_tokens, s);
+    if (dtype == DT_F32) return pick_recurrence<float>(pp, n_items, n_tokens, s);
+    if (dtype == DT_BF16) return pick_recurrence<bf16>(pp, n_items, n_tokens, s);
     return fail("linear_recurrence: unknown dtype");
 }
 

@@ -295,9 +295,11 @@ def test_taps_kernel_with_bias_and_activation_over_cuts():
 
 
 @pytest.mark.parametrize("heads, qk_heads, dim, vdim", [(2, 1, 12, 37), (3, 3, 40, 8), (4, 2, 70, 33), (1, 1, 130, 20),
-                                                        (2, 2, 300, 6)])
+                                                        (2, 2, 300, 6), (60, 2, 40, 70), (80, 2, 40, 70), (60, 3, 100, 40),
+                                                        (80, 4, 100, 40)])
 def test_recurrence_kernel_carries_its_state(heads, qk_heads, dim, vdim):
-    """Both forms, a sequence cut in six (down to one token), against the token-by-token formulas."""
+    """Both forms, a sequence cut in six (down to one token), against the token-by-token formulas.
+    (With 60 and 80 heads a thread of the kernel takes four and eight columns of the state.)"""
     from mini_llm_b200.kernels import ops
     rng = np.random.default_rng(dim)
     n = 100
