@@ -723,22 +723,20 @@ static int pick_recurrence(const RecurrenceParams& pp, int n_items, int n_tokens
         if (pp.dim <= 128) return launch_recurrence<T, 32, 4, 16, 1>(pp, n_items, s);
     } else if (pp.dim <= 128) {
         // Prompt portions.  The walk from token to token is a chain of dependent sums and exchanges
-        // between lanes, about as long whatever a thread holds; so a thread takes 2, 4 or 8 columns,
-        // whose chains run in one another's gaps: the fewest that leave the busy entries' blocks
-        // (entries of a step that is filled up to a round shape may be empty) one an SM.
+        // between lanes; a thread takes two columns, whose chains run in one another's gaps, or four
+        // where two would leave the busy entries' blocks more than one an SM (entries of a step that
+        // is filled up to a round shape may be empty: portions are taken to hold 512 tokens).
+        // Eight columns a thread measured slower: every column has its own exchanges.
         const int groups = pp.dim <= 64 ? 16 : 8;
-        int busy = (n_tokens + 255) / 256;
+        int busy = (n_tokens + 511) / 512;
         if (busy > n_items) busy = n_items;
-        int columns = 2;
-        while (columns < 8 && (long)busy * pp.heads * ((pp.vdim + groups * columns - 1) / (groups * columns)) > 148) columns *= 2;
+        const bool four = (long)busy * pp.heads * ((pp.vdim + groups * 2 - 1) / (groups * 2)) > 148;
         if (pp.dim <= 64) {
-            if (columns == 2) return launch_recurrence<T, 8, 8, 16, 2>(pp, n_items, s);
-            if (columns == 4) return launch_recurrence<T, 8, 8, 16, 4>(pp, n_items, s);
-            return launch_recurrence<T, 8, 8, 16, 8>(pp, n_items, s);
+            if (four) return launch_recurrence<T, 8, 8, 16, 4>(pp, n_items, s);
+            return launch_recurrence<T, 8, 8, 16, 2>(pp, n_items, s);
         }
-        if (columns == 2) return launch_recurrence<T, 8, 16, 16, 2>(pp, n_items, s);
-        if (columns == 4) return launch_recurrence<T, 8, 16, 16, 4>(pp, n_items, s);
-        return launch_recurrence<T, 8, 16, 16, 8>(pp, n_items, s);
+        if (four) return launch_recurrence<T, 8, 16, 16, 4>(pp, n_items, s);
+        return launch_recurrence<T, 8, 16, 16, 2>(pp, n_items, s);
     }
     if (pp.dim <= 256) return launch_recurrence<T, 8, 32, 16, 2>(pp, n_items, s);
     return launch_recurrence<T, 32, 32, 4, 1>(pp, n_items, s);

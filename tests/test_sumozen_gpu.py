@@ -299,7 +299,7 @@ def test_taps_kernel_with_bias_and_activation_over_cuts():
                                                         (80, 4, 100, 40)])
 def test_recurrence_kernel_carries_its_state(heads, qk_heads, dim, vdim):
     """Both forms, a sequence cut in six (down to one token), against the token-by-token formulas.
-    (With 60 and 80 heads a thread of the kernel takes four and eight columns of the state.)"""
+    (With 60 and 80 heads a thread of the kernel takes four columns of the state.)"""
     from mini_llm_b200.kernels import ops
     rng = np.random.default_rng(dim)
     n = 100
@@ -337,8 +337,9 @@ def test_recurrence_kernel_carries_its_state(heads, qk_heads, dim, vdim):
                                   dev([0, 1], torch.int32), dev([0, 0], torch.int32), dev([0, count], torch.int32), heads,
                                   qk_heads, dim, vdim, delta, unit_norm=delta, q_scale=0.5 if delta else 1.0,
                                   skip=None if delta else dev(skip))
-        np.testing.assert_allclose(out.cpu().numpy(), expected.reshape(n, heads * vdim), rtol=5e-5, atol=2e-5,
-                                   err_msg=f"delta {delta}")
+        # (32-bit sums: an entry's rounding follows the largest values that went into it, not its own)
+        np.testing.assert_allclose(out.cpu().numpy(), expected.reshape(n, heads * vdim), rtol=5e-5,
+                                   atol=5e-6 * max(4.0, float(np.abs(expected).max())), err_msg=f"delta {delta}")
         assert float(state[0].abs().max()) == 0.0
 
 
