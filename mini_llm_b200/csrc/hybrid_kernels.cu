@@ -725,10 +725,10 @@ static int pick_recurrence(const RecurrenceParams& pp, int n_items, int n_tokens
         // Prompt portions.  The walk from token to token is a chain of dependent sums and exchanges
         // between lanes; a thread takes two columns, whose chains run in one another's gaps, or four
         // where two would leave the busy entries' blocks more than one an SM (entries of a step that
-        // is filled up to a round shape may be empty: portions are taken to hold 512 tokens).
+        // is filled up to a round shape may be empty: portions are taken to hold 1,024 tokens).
         // Eight columns a thread measured slower: every column has its own exchanges.
         const int groups = pp.dim <= 64 ? 16 : 8;
-        int busy = (n_tokens + 511) / 512;
+        int busy = (n_tokens + 1023) / 1024;
         if (busy > n_items) busy = n_items;
         const bool four = (long)busy * pp.heads * ((pp.vdim + groups * 2 - 1) / (groups * 2)) > 148;
         if (pp.dim <= 64) {
